@@ -4,8 +4,9 @@ for the layers that keep that.
 
 Layers with the same need form a group with storage of its own:
   * a KV group: pool[layer, page, 2 (K, V), kv head, row, head_dim] in the
-    model's dtype, pages of ``page_size`` tokens handed out on demand; a group
-    with a window gives pages back as they fall out of it;
+    model's dtype (one flat row a page where keys and values differ in size or
+    the values lie inside the keys' rows), pages of ``page_size`` tokens handed
+    out on demand; a group with a window gives pages back as they fall out of it;
   * a state group: state[layer, slot, ...] in the need's dtype (float32 unless it
     says otherwise), zeroed when the slot is assigned.
 The reference allocates keys and values only for its attention layers through
@@ -142,7 +143,7 @@ class SequenceCache:
         for gi, g in enumerate(plan.groups):
             if isinstance(g.need, KVNeed):
                 if g.need.uneven:
-                    shape = (g.n_layers, max(n_pages, 1), g.need.n_kv_heads * page_size * (g.need.head_dim + g.need.value_dim))
+                    shape = (g.n_layers, max(n_pages, 1), g.need.page_elements(page_size))
                 else:
                     shape = (g.n_layers, max(n_pages, 1), 2, g.need.n_kv_heads, page_size, g.need.head_dim)
                 self.storage[gi] = torch.zeros(shape, dtype=dtype, device=self.device)
@@ -339,7 +340,10 @@ class SequenceCache:
                     if page is None or lo >= hi:
                         continue
                     ks[:, lo:hi] = st[:, page, :nkv * ps * dk].view(-1, nkv, ps, dk)[:, :, :hi - lo].permute(0, 2, 1, 3)
-                    vs[:, lo:hi] = st[:, page, nkv * ps * dk:].view(-1, nkv, ps, dv)[:, :, :hi - lo].permute(0, 2, 1, 3)
+                    if g.need.values_in_keys:
+                        vs[:, lo:hi] = ks[:, lo:hi, :, :dv]
+                    else:
+                        vs[:, lo:hi] = st[:, page, nkv * ps * dk:].view(-1, nkv, ps, dv)[:, :, :hi - lo].permute(0, 2, 1, 3)
                 out[gi] = (ks, vs)
             elif isinstance(g.need, KVNeed):
                 L = int(self._len[slot])

@@ -18,13 +18,16 @@ class KVNeed:
     of another size than the keys' ``head_dim``; a page is then one flat row, the keys [kv head][row][head_dim]
     followed by the values [kv head][row][v_dim].  ``chunk`` > 0 (instead of a window): a token reads only the
     keys of its own chunk of ``chunk`` positions, counted from the sequence's start, so the pages that lie wholly
-    before the chunk of the next token are given back."""
+    before the chunk of the next token are given back.  ``values_in_keys``: the values are the first ``v_dim``
+    elements of the keys' rows (a compressed cache that all heads read), so a page holds rows only:
+    [kv head][row][head_dim]."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
     v_dim: int = 0
     keep_first: int = 0
     chunk: int = 0
+    values_in_keys: bool = False
 
     @property
     def value_dim(self) -> int:
@@ -32,7 +35,12 @@ class KVNeed:
 
     @property
     def uneven(self) -> bool:
-        return self.value_dim != self.head_dim
+        return self.values_in_keys or self.value_dim != self.head_dim
+
+    def page_elements(self, page_size: int) -> int:
+        """Elements of one layer's page when it is one flat row (``uneven``)."""
+        per_row = self.head_dim if self.values_in_keys else self.head_dim + self.value_dim
+        return self.n_kv_heads * page_size * per_row
 
 
 @dataclass(frozen=True)

@@ -299,3 +299,80 @@ MV_API int mv_delay(long long us, cudaStream_t stream) {
     delay_kernel<<<1, 1, 0, stream>>>((unsigned long long)us * 1000ull);
     return mv_launch_status();
 }
+
+// ------------------------------------------------- token embedding plus a hashed bigram row
+// x = table[token] + bigram[r], r = (previous token * mul_prev + token * mul_cur) mod buckets, or row `buckets`
+// (the table's last) for the token at position 0.  The previous token of a step's first token is what the
+// sequence kept (prev[slot]); the block of a sequence's first row in the step also writes the sequence's last
+// token of the step there, after it has read the old one.  ``kept`` (or null) gets a second copy of the rows.
+template <typename T>
+__global__ void embed_bigram_kernel(const T* __restrict__ table, const T* __restrict__ bigram, const int* __restrict__ tok,
+                                    const int* __restrict__ positions, const int* __restrict__ seq_of,
+                                    const int* __restrict__ cu, const int* __restrict__ slots, int* __restrict__ prev,
+                                    float* __restrict__ x, float* __restrict__ kept, int H, int buckets,
+                                    long long mul_prev, long long mul_cur) {
+    mv_pdl_begin();
+    __shared__ int row_s;
+    const int n = blockIdx.x;
+    if (threadIdx.x == 0) {
+        const int b = seq_of[n];
+        const bool first = n == cu[b];
+        const bool slot_ok = mv_slot_ok(slots[b]);
+        const int slot = slot_ok ? slots[b] : 0;
+        const int before = first ? prev[slot] : tok[n - 1];
+        int r = buckets;
+        if (positions[n] > 0) {
+            long long v = ((long long)before * mul_prev + (long long)tok[n] * mul_cur) % (long long)buckets;
+            if (v < 0) v += buckets;
+            r = (int)v;
+        }
+        row_s = r;
+        if (first && slot_ok) prev[slot] = tok[cu[b + 1] - 1];
+    }
+    __syncthreads();
+    const T* row = table + (size_t)tok[n] * H;
+    const T* brow = bigram + (size_t)row_s * H;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float v = mv_to_f32(row[h]) + mv_to_f32(brow[h]);
+        x[(size_t)n * H + h] = v;
+        if (kept) kept[(size_t)n * H + h] = v;
+    }
+}
+
+MV_GUARD_SETTER(elementwise)
+
+MV_API int mv_embed_bigram(const void* table, const void* bigram, int table_dtype, const int* tok, const int* positions,
+                           const int* seq_of, const int* cu, const int* slots, int* prev, float* x, float* kept, int N,
+                           int H, int buckets, long long mul_prev, long long mul_cur, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (buckets < 1) return (int)cudaErrorInvalidValue;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == MV_DT_BF16)
+        mv_launch(embed_bigram_kernel<__nv_bfloat16>, N, threads, 0, stream, (const __nv_bfloat16*)table,
+                  (const __nv_bfloat16*)bigram, tok, positions, seq_of, cu, slots, prev, x, kept, H, buckets, mul_prev, mul_cur);
+    else
+        mv_launch(embed_bigram_kernel<float>, N, threads, 0, stream, (const float*)table, (const float*)bigram, tok,
+                  positions, seq_of, cu, slots, prev, x, kept, H, buckets, mul_prev, mul_cur);
+    return mv_launch_status();
+}
+
+// x[n, :] += rows[n, :] (or nothing if null) + vec[:] (or nothing if null): what a pass over a run of layers adds
+// to the stream before its first layer.
+__global__ void __launch_bounds__(256)
+add_rows_vector_kernel(float* __restrict__ x, const float* __restrict__ rows, const float* __restrict__ vec, long long total,
+                       int H) {
+    mv_pdl_begin();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    float v = x[idx];
+    if (rows) v += rows[idx];
+    if (vec) v += vec[idx % H];
+    x[idx] = v;
+}
+
+MV_API int mv_add_rows_vector(float* x, const float* rows, const float* vec, int N, int H, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    const long long total = (long long)N * H;
+    mv_launch(add_rows_vector_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, x, rows, vec, total, H);
+    return mv_launch_status();
+}

@@ -1,4 +1,4 @@
-// Row-wise pieces that sit between matrix products: a layer norm without bias, a root-mean-square
+// Row-wise pieces that sit between matrix products: a layer norm (with or without a bias), a root-mean-square
 // norm over groups of a row followed by a gate, a root-mean-square norm whose result is added to
 // the residual stream, a clamped gated activation, a gate by a per-token table row, and the
 // rounding of 32-bit rows to the model's dtype.  Statistics and activations are 32-bit whatever
@@ -6,11 +6,11 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- layer norm
-// y[i, :] = (x[r, :] - mean) / sqrt(mean((x - mean)^2) + eps) * w, r = rows ? rows[i] : i.  Two passes
+// y[i, :] = (x[r, :] - mean) / sqrt(mean((x - mean)^2) + eps) * w (+ b), r = rows ? rows[i] : i.  Two passes
 // over the row for the statistics (the variance is the mean of the squared deviations).
 template <typename TO>
-__global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ y,
-                                 const int* __restrict__ rows, int H, float eps) {
+__global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                                 TO* __restrict__ y, const int* __restrict__ rows, int H, float eps) {
     mv_pdl_begin();
     __shared__ float scratch[33];
     const int i = blockIdx.x;
@@ -26,17 +26,19 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
     }
     const float scale = 1.0f / sqrtf(mv_block_sum(ss, scratch) / (float)H + eps);
     TO* yr = y + (size_t)i * H;
-    for (int h = threadIdx.x; h < H; h += blockDim.x) yr[h] = mv_from_f32<TO>((xr[h] - mean) * scale * w[h]);
+    for (int h = threadIdx.x; h < H; h += blockDim.x)
+        yr[h] = mv_from_f32<TO>(fmaf((xr[h] - mean) * scale, w[h], b ? b[h] : 0.f));
 }
 
-MV_API int mv_layernorm(const float* x, const float* w, void* y, int y_dtype, const int* rows, int n_rows, int H,
-                        float eps, cudaStream_t stream) {
+// b: the bias [H], or null for none
+MV_API int mv_layernorm(const float* x, const float* w, const float* b, void* y, int y_dtype, const int* rows, int n_rows,
+                        int H, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (y_dtype == MV_DT_BF16)
-        mv_launch(layernorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, w, (__nv_bfloat16*)y, rows, H, eps);
+        mv_launch(layernorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, w, b, (__nv_bfloat16*)y, rows, H, eps);
     else
-        mv_launch(layernorm_kernel<float>, n_rows, threads, 0, stream, x, w, (float*)y, rows, H, eps);
+        mv_launch(layernorm_kernel<float>, n_rows, threads, 0, stream, x, w, b, (float*)y, rows, H, eps);
     return mv_launch_status();
 }
 

@@ -1,6 +1,7 @@
-// Routing of a mixture of experts whose scores are sigmoids, and the gated activation of the chosen experts.
+// Routing of a mixture of experts, and the gated activation of the chosen experts.
 //
-// Router: s_e = sigmoid(z_e) from 32-bit logits.  The experts form `n_groups` equal groups of neighbours; a
+// Router: s_e = sigmoid(z_e) from 32-bit logits, or softmax over all of them; a correction per expert may be added
+// for the choice alone; some of the routed entries may be identity experts (no matrices: their output is their input).  The experts form `n_groups` equal groups of neighbours; a
 // group's score is the sum of its two largest s (of its only one, in groups of one); only experts of the
 // `keep` best groups can be chosen; the `top` largest s among those are chosen; their weights are s divided
 // by the sum of the chosen s (+ 1e-20).  Ties go to the lower index.  A shared expert's gate, sigmoid of one
@@ -21,84 +22,137 @@ __device__ __forceinline__ void re_argmax(float& v, int& i) {
     }
 }
 
-// one warp a token
+// one warp a token.  mode 0: scores sigmoid(z); mode 1: scores softmax(z) over all E routed entries.  `correction`
+// (or null) is added to the scores for the CHOICE only; the weights are the chosen entries' own scores over their sum
+// (+ 1e-20), times out_scale.  The last n_identity of the E entries are identity experts: the dense row is laid out
+// [E - n_identity experts | the shared gate, if any | n_identity identity weights].
 __global__ void __launch_bounds__(128)
 route_kernel(const float* __restrict__ z, int ld, float* __restrict__ dense, int* __restrict__ pick,
-             float* __restrict__ pick_w, int N, int E, int n_groups, int keep, int top, int shared_gate) {
+             float* __restrict__ pick_w, int N, int E, int n_groups, int keep, int top, int shared_gate, int mode,
+             const float* __restrict__ correction, float out_scale, int n_identity) {
     mv_pdl_begin();
     extern __shared__ float re_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * (blockDim.x >> 5) + warp;
     if (n >= N) return;
-    float* s = re_smem + (size_t)warp * (E + n_groups);       // scores; -1 once taken or not allowed
-    float* gs = s + E;                                        // group scores
+    const float NEG = -3.0e38f;
+    float* s = re_smem + (size_t)warp * (2 * E + n_groups);   // scores
+    float* ch = s + E;                                        // choice scores; NEG once taken or not allowed
+    float* gs = ch + E;                                       // group scores
     const float* zr = z + (size_t)n * ld;
-    const int cols = E + (shared_gate ? 1 : 0);
+    const int n_real = E - n_identity, sg = shared_gate ? 1 : 0;
+    const int cols = E + sg;
     float* dr = dense + (size_t)n * cols;
-    for (int e = lane; e < E; e += 32) {
-        s[e] = 1.0f / (1.0f + expf(-zr[e]));
-        dr[e] = 0.f;
+    if (mode == 1) {
+        float mx = NEG;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zr[e]);
+        mx = mv_warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) {
+            const float v = expf(zr[e] - mx);
+            s[e] = v;
+            sum += v;
+        }
+        sum = mv_warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < E; e += 32) s[e] *= inv;
+    } else {
+        for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-zr[e]));
     }
-    if (shared_gate && lane == 0) dr[E] = 1.0f / (1.0f + expf(-zr[E]));
+    for (int e = lane; e < E; e += 32) ch[e] = s[e] + (correction ? correction[e] : 0.f);
+    for (int c = lane; c < cols; c += 32) dr[c] = 0.f;
     __syncwarp();
+    if (shared_gate && lane == 0) dr[n_real] = 1.0f / (1.0f + expf(-zr[E]));
     const int per = E / n_groups;
     if (keep < n_groups) {
         for (int g = lane; g < n_groups; g += 32) {
-            float a = -1.f, b = -1.f;                          // the two largest of the group
+            float a = NEG, b = NEG;                            // the two largest of the group
             for (int e = g * per; e < (g + 1) * per; ++e) {
-                const float v = s[e];
+                const float v = ch[e];
                 if (v > a) { b = a; a = v; } else if (v > b) b = v;
             }
             gs[g] = a + (per > 1 ? b : 0.f);
         }
         __syncwarp();
-        // the best `keep` groups keep a score >= 0 in gs; then the others' experts are struck out
+        // the best `keep` groups are marked; then the others' experts are struck out
         for (int r = 0; r < keep; ++r) {
-            float v = -1.f; int i = 0x7fffffff;
+            float v = NEG; int i = 0x7fffffff;
             for (int g = lane; g < n_groups; g += 32)
                 if (gs[g] > v) { v = gs[g]; i = g; }
             re_argmax(v, i);
-            if (lane == 0) gs[i] = -2.f;                       // chosen
+            if (lane == 0) gs[i] = 2.f * NEG;                  // chosen
             __syncwarp();
         }
         for (int e = lane; e < E; e += 32)
-            if (gs[e / per] != -2.f) s[e] = -1.f;
+            if (gs[e / per] != 2.f * NEG) ch[e] = NEG;
         __syncwarp();
     }
     float sum = 0.f;
     for (int r = 0; r < top; ++r) {
-        float v = -1.f; int i = 0x7fffffff;
+        float v = NEG; int i = 0x7fffffff;
         for (int e = lane; e < E; e += 32)
-            if (s[e] > v) { v = s[e]; i = e; }
+            if (ch[e] > v) { v = ch[e]; i = e; }
         re_argmax(v, i);
-        sum += v;
+        const float sc = s[i];
+        sum += sc;
         if (lane == 0) {
             pick[(size_t)n * top + r] = i;
-            pick_w[(size_t)n * top + r] = v;
-            s[i] = -1.f;
+            pick_w[(size_t)n * top + r] = sc;
+            ch[i] = NEG;
         }
         __syncwarp();
     }
-    const float inv = 1.0f / (sum + 1e-20f);
+    const float inv = out_scale / (sum + 1e-20f);
     if (lane < top) {
         // (top <= 32 is checked by the host)
         const float w = pick_w[(size_t)n * top + lane] * inv;
         pick_w[(size_t)n * top + lane] = w;
-        dr[pick[(size_t)n * top + lane]] = w;
+        const int i = pick[(size_t)n * top + lane];
+        dr[i < n_real ? i : i + sg] = w;
     }
 }
 
-// z [N, >= E (+ 1)] with row stride ld; dense [N, E (+ 1)]; pick, pick_w [N, top].
+// z [N, >= E (+ 1)] with row stride ld; dense [N, E (+ 1)]; pick, pick_w [N, top]; correction [E] or null.
 MV_API int mv_route(const float* z, int ld, float* dense, int* pick, float* pick_w, int N, int E, int n_groups,
-                    int keep, int top, int shared_gate, cudaStream_t stream) {
+                    int keep, int top, int shared_gate, int mode, const float* correction, float out_scale,
+                    int n_identity, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (E < 1 || E > RE_MAX_EXPERTS || n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups || top < 1 ||
-        top > 32 || top > keep * (E / n_groups))
+        top > 32 || top > keep * (E / n_groups) || n_identity < 0 || n_identity > E || mode < 0 || mode > 1)
         return (int)cudaErrorInvalidValue;
     const int warps = 4;
-    const size_t smem = sizeof(float) * warps * (size_t)(E + n_groups);
+    const size_t smem = sizeof(float) * warps * (size_t)(2 * E + n_groups);
     mv_launch(route_kernel, (N + warps - 1) / warps, warps * 32, smem, stream, z, ld, dense, pick, pick_w, N, E,
-              n_groups, keep, top, shared_gate);
+              n_groups, keep, top, shared_gate, mode, correction, out_scale, n_identity);
+    return mv_launch_status();
+}
+
+// resid[n, :] += (sum of dense[n, col0 .. col0 + n_cols)) * h[n, :]: experts whose output is their input.
+template <typename T>
+__global__ void __launch_bounds__(256)
+identity_experts_kernel(const T* __restrict__ h, const float* __restrict__ dense, int ld, int col0, int n_cols,
+                        float* __restrict__ resid, long long total, int H, int accumulate) {
+    mv_pdl_begin();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long long n = idx / H;
+    float w = 0.f;
+    for (int c = 0; c < n_cols; ++c) w += dense[n * ld + col0 + c];
+    const float v = w * mv_to_f32(h[idx]);
+    resid[idx] = accumulate ? resid[idx] + v : v;
+}
+
+MV_API int mv_identity_experts(const void* h, int dtype, const float* dense, int ld, int col0, int n_cols, float* resid,
+                               int N, int H, int accumulate, cudaStream_t stream) {
+    if (N <= 0 || n_cols <= 0) return 0;
+    const long long total = (long long)N * H;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == MV_DT_BF16)
+        mv_launch(identity_experts_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)h, dense, ld, col0,
+                  n_cols, resid, total, H, accumulate);
+    else
+        mv_launch(identity_experts_kernel<float>, blocks, 256, 0, stream, (const float*)h, dense, ld, col0, n_cols, resid,
+                  total, H, accumulate);
     return mv_launch_status();
 }
 
@@ -130,10 +184,11 @@ routed_glu_kernel(const float* __restrict__ gu, const float* __restrict__ dense,
     hid[idx] = mv_from_f32<TO>(out);
 }
 
+// extra_cols: columns of a dense row after the experts' (and the shared gate's) that belong to others
 MV_API int mv_routed_glu(const float* gu, const float* dense, void* hid, int hid_dtype, int N, int E, int ff,
-                         int shared_ff, int group, int shared_group, cudaStream_t stream) {
+                         int shared_ff, int group, int shared_group, int extra_cols, cudaStream_t stream) {
     if (N <= 0) return 0;
-    const int F = E * ff + shared_ff, cols = E + (shared_ff ? 1 : 0);
+    const int F = E * ff + shared_ff, cols = E + (shared_ff ? 1 : 0) + extra_cols;
     if ((group && ff % group) || (shared_group && shared_ff % shared_group)) return (int)cudaErrorInvalidValue;
     const long long total = (long long)N * F;
     const unsigned blocks = (unsigned)((total + 255) / 256);
@@ -309,9 +364,9 @@ scale_expert_columns_kernel(T* __restrict__ h, const float* __restrict__ dense, 
 }
 
 MV_API int mv_scale_expert_columns(void* h, int dtype, const float* dense, int N, int E, int ff, int shared_ff,
-                                   cudaStream_t stream) {
+                                   int extra_cols, cudaStream_t stream) {
     if (N <= 0) return 0;
-    const int F = E * ff + shared_ff, cols = E + (shared_ff ? 1 : 0);
+    const int F = E * ff + shared_ff, cols = E + (shared_ff ? 1 : 0) + extra_cols;
     const long long total = (long long)N * F;
     const bool wide = ff % 8 == 0 && shared_ff % 8 == 0 && ((uintptr_t)h % 16) == 0;
     const unsigned blocks = (unsigned)((total / (wide ? 8 : 1) + 255) / 256);

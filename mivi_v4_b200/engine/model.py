@@ -94,8 +94,14 @@ class Model:
 
     # ---- cache --------------------------------------------------------------
     def cache_plan(self) -> CachePlan:
+        """One position per schedule entry; an embedding that keeps something per sequence (the previous token)
+        has the position after the last entry."""
         needs = [self.blocks[e.block].cache_need() for e in self.schedule]
-        return plan_cache(needs, [e.cache_of for e in self.schedule])
+        cache_of = [e.cache_of for e in self.schedule]
+        if self.embedding.cache_need() is not None:
+            needs.append(self.embedding.cache_need())
+            cache_of.append(None)
+        return plan_cache(needs, cache_of)
 
     # ---- one step ---------------------------------------------------------------
     def forward(self, step, cache) -> Optional[torch.Tensor]:
@@ -111,6 +117,8 @@ class Model:
             if link is not None:
                 x = self.embedding.forward(step, emit=link)
                 step.leave_link(link)
+            elif self.embedding.cache_need() is not None:
+                x = self.embedding.forward(step, cache.view(len(self.schedule), step.page_tables))
             else:
                 x = self.embedding.forward(step)
         for pos, entry in enumerate(self.schedule):

@@ -45,7 +45,7 @@ _SIGNATURES = {
         "mv_attention_generic": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
         "mv_attention_decode": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I,
                                 _I, _I, _P],
-        "mv_layernorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
+        "mv_layernorm": [_P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
         "mv_gated_rmsnorm": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
         "mv_rmsnorm_add": [_P, _P, _P, _I, _I, _F, _P],
         "mv_rmsnorm_add_layernorm": [_P, _P, _F, _P, _P, _F, _P, _I, _I, _I, _P],
@@ -73,9 +73,16 @@ _SIGNATURES = {
         "mv_causal_conv_silu": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "mv_ssm_decode_prepare": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P],
         "mv_step_size": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
-        "mv_route": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-        "mv_routed_glu": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-        "mv_scale_expert_columns": [_P, _I, _P, _I, _I, _I, _I, _P],
+        "mv_route": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
+        "mv_routed_glu": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+        "mv_scale_expert_columns": [_P, _I, _P, _I, _I, _I, _I, _I, _P],
+        "mv_identity_experts": [_P, _I, _P, _I, _I, _I, _P, _I, _I, _I, _P],
+        "mv_embed_bigram": [_P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _Q, _Q, _P],
+        "mv_add_rows_vector": [_P, _P, _P, _I, _I, _P],
+        "mv_latent_prepare": [_P, _I, _I, _I, _P, _F, _P, _P, _P, _P, _I, _I, _P, _Q, _I, _P, _I, _I, _I, _I, _I, _I, _P],
+        "mv_head_product": [_P, _Q, _I, _P, _I, _I, _P, _Q, _P, _I, _Q, _I, _I, _I, _I, _I, _P],
+        "mv_latent_attention": [_P, _P, _Q, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+        "mv_delta_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _F, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "mv_expert_rank": [_P, _I, _I, _P, _P, _P],
         "mv_expert_gather": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
         "mv_expert_tiles": [_P, _I, _I, _P, _P, _I, _P],
@@ -370,14 +377,14 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
 
 
 def layernorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
-              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[i] = (x[r] - mean) / sqrt(var + eps) * w with r = rows[i] or i; no bias; statistics in float32,
+              rows: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = (x[r] - mean) / sqrt(var + eps) * w (+ bias) with r = rows[i] or i; statistics in float32,
     the variance being the mean of the squared deviations."""
     H = x.shape[-1]
     n = rows.numel() if rows is not None else x.shape[0]
     _check(_fn("core", "mv_layernorm")(
         _need(x, "layernorm x", torch.float32), _need(w, "layernorm weight", torch.float32, (H,)),
-        _need(out, "layernorm out", None, (n, H)), _dt(out),
+        _need(bias, "layernorm bias", torch.float32, (H,), True), _need(out, "layernorm out", None, (n, H)), _dt(out),
         _need(rows, "layernorm rows", torch.int32, optional=True), n, H, float(eps), _stream()), "mv_layernorm")
     account(n * H * (4 + out.element_size()))
     return out
@@ -664,30 +671,53 @@ def ssm_decode_prepare(u: torch.Tensor, taps: torch.Tensor, bias: Optional[torch
 MAX_EXPERTS = 1024
 
 
+ROUTE_SIGMOID, ROUTE_SOFTMAX = 0, 1
+
+
 def route(z: torch.Tensor, dense: torch.Tensor, pick: torch.Tensor, pick_w: torch.Tensor, n_experts: int,
-          n_groups: int, keep: int, top: int, shared_gate: bool) -> None:
-    """Router of a mixture of experts from float32 logits ``z`` [N, experts (+ 1)]: scores sigmoid(z); the experts
+          n_groups: int, keep: int, top: int, shared_gate: bool, *, mode: int = ROUTE_SIGMOID,
+          correction: Optional[torch.Tensor] = None, out_scale: float = 1.0, n_identity: int = 0) -> None:
+    """Router of a mixture of experts from float32 logits ``z`` [N, routed (+ 1)]: scores sigmoid(z), or with
+    ``ROUTE_SOFTMAX`` softmax(z) over all routed entries; the entries
     form ``n_groups`` equal groups of neighbours whose score is the sum of their two largest scores; among the
-    experts of the ``keep`` best groups the ``top`` largest are chosen, with weights score / (sum of the chosen
-    scores + 1e-20).  ``dense`` [N, experts (+ 1)] gets a row of weights (zero where not chosen; with
-    ``shared_gate`` the last column is sigmoid of the last logit), ``pick`` / ``pick_w`` [N, top] the lists."""
+    entries of the ``keep`` best groups the ``top`` largest are chosen, with weights score / (sum of the chosen
+    scores + 1e-20) * ``out_scale``.  ``correction`` [routed] is added to the scores for the choice only.
+    ``n_experts`` counts all routed entries; its last ``n_identity`` are identity experts.  ``dense``
+    [N, routed (+ 1)] gets a row of weights (zero where not chosen), laid out [experts | with ``shared_gate``
+    sigmoid of the last logit | identity experts]; ``pick`` / ``pick_w`` [N, top] the lists (routed indices)."""
     N = dense.shape[0]
     E = int(n_experts)
     cols = E + (1 if shared_gate else 0)
     if (E < 1 or E > MAX_EXPERTS or n_groups < 1 or E % n_groups or not 1 <= keep <= n_groups or not 1 <= top <= 32
-            or top > keep * (E // n_groups)):
+            or top > keep * (E // n_groups) or not 0 <= n_identity <= E):
         raise KernelError(f"route: {E} experts in {n_groups} groups, {keep} groups kept, {top} chosen: not a routing "
                           f"this kernel takes (at most {MAX_EXPERTS} experts, 32 chosen)")
     zp, ldz = _cols(z, "router logits", N, cols)
     _check(_fn("core", "mv_route")(
         zp, ldz, _need(dense, "route weights", torch.float32, (N, cols)), _need(pick, "route picks", torch.int32, (N, top)),
         _need(pick_w, "route pick weights", torch.float32, (N, top)), N, E, int(n_groups), int(keep), int(top),
-        int(bool(shared_gate)), _stream()), "mv_route")
+        int(bool(shared_gate)), int(mode), _need(correction, "route correction", torch.float32, (E,), True),
+        float(out_scale), int(n_identity), _stream()), "mv_route")
     account(N * cols * 8)
 
 
+def identity_experts(h: torch.Tensor, dense: torch.Tensor, col0: int, n_cols: int, resid: torch.Tensor,
+                     accumulate: bool = True) -> torch.Tensor:
+    """resid[n] (+)= (dense[n, col0] + ... + dense[n, col0 + n_cols - 1]) * h[n]: the experts whose output is
+    their input, with the router's weights from its dense rows."""
+    N, H = h.shape
+    if dense.dim() != 2 or dense.shape[0] != N or col0 < 0 or col0 + n_cols > dense.shape[1]:
+        raise KernelError(f"identity_experts: columns {col0}..{col0 + n_cols} of weights {tuple(dense.shape)} for {N} rows")
+    _check(_fn("core", "mv_identity_experts")(
+        _need(h, "identity_experts input"), _dt(h), _need(dense, "route weights", torch.float32), dense.shape[1], int(col0),
+        int(n_cols), _need(resid, "residual stream", torch.float32, (N, H)), N, H, int(bool(accumulate)), _stream()),
+        "mv_identity_experts")
+    account(N * H * (8 + h.element_size()))
+    return resid
+
+
 def routed_glu(gu: torch.Tensor, dense: torch.Tensor, hid: torch.Tensor, n_experts: int, ff: int, shared_ff: int,
-               group: int = 0, shared_group: int = 0) -> torch.Tensor:
+               group: int = 0, shared_group: int = 0, extra_cols: int = 0) -> torch.Tensor:
     """hid[n, c] = weight(n, expert of column c) * silu(gate[n, c]) * up[n, c] over the columns of all experts end to
     end (then a shared expert's), from ``gu`` [N, 2 * F] float32 and the router's dense weights; nothing is computed
     where the weight is zero.  ``gu`` holds each expert's gates and ups together, [e * 2 ff, (e + 1) * 2 ff): the gates,
@@ -700,22 +730,24 @@ def routed_glu(gu: torch.Tensor, dense: torch.Tensor, hid: torch.Tensor, n_exper
         raise KernelError(f"routed_glu: widths {ff} and {shared_ff} against groups of {group} and {shared_group}")
     _check(_fn("core", "mv_routed_glu")(
         _need(gu, "routed_glu input", torch.float32, (N, 2 * F)),
-        _need(dense, "route weights", torch.float32, (N, n_experts + (1 if shared_ff else 0))),
+        _need(dense, "route weights", torch.float32, (N, n_experts + (1 if shared_ff else 0) + extra_cols)),
         _need(hid, "routed_glu out"), _dt(hid), N, int(n_experts), int(ff), int(shared_ff), int(group), int(shared_group),
-        _stream()), "mv_routed_glu")
+        int(extra_cols), _stream()), "mv_routed_glu")
     account(N * F * (8 + hid.element_size()))
     return hid
 
 
-def scale_expert_columns(h: torch.Tensor, dense: torch.Tensor, n_experts: int, ff: int, shared_ff: int) -> torch.Tensor:
+def scale_expert_columns(h: torch.Tensor, dense: torch.Tensor, n_experts: int, ff: int, shared_ff: int,
+                         extra_cols: int = 0) -> torch.Tensor:
     """h[n, c] *= weight(n, expert of column c) in place, over the columns of all experts end to end (then a shared
     expert's): for activations that a product's epilogue has gated already."""
     N, F = h.shape
     if F != n_experts * ff + shared_ff:
         raise KernelError(f"scale_expert_columns: {F} columns for {n_experts} experts of {ff} and a shared one of {shared_ff}")
     _check(_fn("core", "mv_scale_expert_columns")(
-        _need(h, "gated activations"), _dt(h), _need(dense, "route weights", torch.float32, (N, n_experts + (1 if shared_ff else 0))),
-        N, int(n_experts), int(ff), int(shared_ff), _stream()), "mv_scale_expert_columns")
+        _need(h, "gated activations"), _dt(h),
+        _need(dense, "route weights", torch.float32, (N, n_experts + (1 if shared_ff else 0) + extra_cols)),
+        N, int(n_experts), int(ff), int(shared_ff), int(extra_cols), _stream()), "mv_scale_expert_columns")
     account(2 * N * F * h.element_size())
     return h
 
@@ -990,6 +1022,150 @@ def attention_sink_prefill(q: torch.Tensor, pool: torch.Tensor, page_size: int, 
         _need(sinks, "sinks", torch.float32, (nh,), True), gp, ldg, _need(out, "attention out", None, (N, nh * dv)),
         N, n_seqs, nh, nkv, dk, dv, float(scale), float(softcap), int(window), int(keep_first), int(chunk), _stream()),
         "mv_attention_sink_prefill")
+    return out
+
+
+def embed_bigram(table: torch.Tensor, bigram: torch.Tensor, tokens, positions, seq_of, cu, slots, prev: torch.Tensor,
+                 out: torch.Tensor, kept: Optional[torch.Tensor], mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """out[n] = table[token] + bigram[r] in float32, r = (previous token * mul_prev + token * mul_cur) mod buckets with
+    buckets = rows of ``bigram`` - 1, or the last row for a token at position 0.  ``prev`` int32 [slots]: the last
+    token of each sequence before this step; it is brought up to date.  ``kept``: a second copy of the rows, or None."""
+    N = tokens.numel()
+    V, H = table.shape
+    if bigram.dim() != 2 or bigram.shape[1] != H or bigram.shape[0] < 2 or bigram.dtype != table.dtype:
+        raise KernelError(f"embed_bigram: bigram table {tuple(bigram.shape)} {bigram.dtype} beside an embedding "
+                          f"{tuple(table.shape)} {table.dtype}")
+    _guard("core", "elementwise", table.device, n_slots=prev.shape[0])
+    _check(_fn("core", "mv_embed_bigram")(
+        _need(table, "embedding table"), _need(bigram, "bigram table"), _dt(table), _need(tokens, "tokens", torch.int32),
+        _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32), _need(cu, "cu", torch.int32),
+        _need(slots, "slots", torch.int32), _need(prev, "previous tokens", torch.int32),
+        _need(out, "embedding out", torch.float32, (N, H)), _need(kept, "embedding copy", torch.float32, (N, H), True),
+        N, H, bigram.shape[0] - 1, int(mul_prev), int(mul_cur), _stream()), "mv_embed_bigram")
+    account(N * H * (2 * table.element_size() + (8 if kept is not None else 4)))
+    return out
+
+
+def add_rows_vector(x: torch.Tensor, rows: Optional[torch.Tensor], vec: Optional[torch.Tensor]) -> torch.Tensor:
+    """x[n] += rows[n] + vec, all float32 (either may be None)."""
+    N, H = x.shape
+    _check(_fn("core", "mv_add_rows_vector")(
+        _need(x, "stream", torch.float32), _need(rows, "rows", torch.float32, (N, H), True),
+        _need(vec, "vector", torch.float32, (H,), True), N, H, _stream()), "mv_add_rows_vector")
+    account(N * H * (12 if rows is not None else 8))
+    return x
+
+
+def _check_latent_pool(pool: torch.Tensor, page_size: int, width: int, what: str) -> None:
+    if pool.dim() != 2 or pool.shape[1] != page_size * width or not pool.is_cuda or pool.stride(1) != 1:
+        raise KernelError(f"{what}: cache pool shape {tuple(pool.shape)}, expected [pages, {page_size} rows x {width}]")
+    if page_size & (page_size - 1):
+        raise KernelError(f"{what}: page size {page_size} is not a power of two")
+
+
+LATENT_MAX_RANK = 1024
+LATENT_MAX_ROT = 512
+
+
+def latent_prepare(proj: torch.Tensor, q0: int, c0: int, w_c: torch.Tensor, eps: float, inv_freq: Optional[torch.Tensor],
+                   positions, seq_of, page_table, pool: torch.Tensor, page_size: int, qa: torch.Tensor, nh: int, dim: int,
+                   rot: int, rank: int, rot_dims: Optional[int] = None) -> None:
+    """From float32 rows of a fused projection (q at column ``q0``: per head [dim | rot]; the latent at column ``c0``:
+    [rank | rot]): the latent's first ``rank`` numbers over their root mean square times ``w_c``, its last ``rot`` and
+    every head's last ``rot`` of q rotated (their first ``rot_dims``, all by default: element i with i + rot_dims / 2,
+    angle pos * inv_freq[i]; the others pass unchanged); the row [rank + rot]
+    goes into the token's place of its page, the rotated parts of q into the last ``rot`` columns of ``qa``
+    [N, nh, rank + rot] (float32)."""
+    N = qa.shape[0]
+    if (not proj.is_cuda or proj.dtype != torch.float32 or proj.dim() != 2 or proj.shape[0] != N or proj.stride(1) != 1
+            or q0 < 0 or q0 + nh * (dim + rot) > proj.shape[1] or c0 < 0 or c0 + rank + rot > proj.shape[1]):
+        raise KernelError(f"latent_prepare: projection {proj.dtype} {tuple(proj.shape)} does not hold q at {q0} and the "
+                          f"latent at {c0} for {N} rows")
+    rot_dims = rot if rot_dims is None else int(rot_dims)
+    if rot_dims % 2 or not 0 <= rot_dims <= rot <= LATENT_MAX_ROT or not 1 <= rank <= LATENT_MAX_RANK:
+        raise KernelError(f"latent_prepare: rank {rank} (1..{LATENT_MAX_RANK}), {rot_dims} of {rot} (<= {LATENT_MAX_ROT}) "
+                          f"elements rotated (an even number)")
+    _check_latent_pool(pool, page_size, rank + rot, "latent_prepare")
+    _guard("core", "latent_attention", proj.device, n_pages=pool.shape[0])
+    _check(_fn("core", "mv_latent_prepare")(
+        proj.data_ptr(), proj.stride(0), int(q0), int(c0), _need(w_c, "latent norm weight", torch.float32, (rank,)),
+        float(eps), _need(inv_freq, "inv_freq", torch.float32, (rot_dims // 2,), rot_dims == 0),
+        _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
+        _need(page_table, "page table", torch.int32), page_table.shape[1], int(page_size), pool.data_ptr(), pool.stride(0),
+        _dt(pool), _need(qa, "absorbed q", torch.float32, (N, nh, rank + rot)), N, nh, dim, rot, rank, rot_dims, _stream()),
+        "mv_latent_prepare")
+    account(N * (nh * rot * 8 + (rank + rot) * (4 + pool.element_size())))
+
+
+def head_product(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, nh: int, n_in: int, n_out: int, *,
+                 transposed: bool = False, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One small matrix per head: y[n, h, :n_out] = W_h x[n, h, :n_in] with ``w`` [nh * n_out, n_in], or with
+    ``transposed`` W_h^T x with ``w`` [nh * n_in, n_out].  ``x`` float32 [N, nh, >= n_in] and ``y`` [N, nh, >= n_out]
+    (float32 or the model's dtype) may be views with any row and head strides.  ``gate``: float32 logits
+    [N, nh * n_out] (a column slice is fine); the result is multiplied by sigmoid(gate)."""
+    N = x.shape[0]
+    for t, what, width in ((x, "input", n_in), (y, "output", n_out)):
+        if not t.is_cuda or t.dim() != 3 or t.shape[0] != N or t.shape[1] != nh or t.shape[2] < width or t.stride(2) != 1:
+            raise KernelError(f"head_product: {what} {tuple(t.shape)} strides {t.stride()} for {N} rows, {nh} heads of {width}")
+    if x.dtype != torch.float32:
+        raise KernelError(f"head_product: input is {x.dtype}, expected float32")
+    rows, cols = (nh * n_in, n_out) if transposed else (nh * n_out, n_in)
+    gp, ldg = _cols(gate, "head_product gate", N, nh * n_out) if gate is not None else (None, 0)
+    _check(_fn("core", "mv_head_product")(
+        x.data_ptr(), x.stride(0), x.stride(1), _need(w, "head matrices", None, (rows, cols)), _dt(w), int(bool(transposed)),
+        gp, ldg, y.data_ptr(), _dt(y), y.stride(0), y.stride(1), N, nh, int(n_in), int(n_out), _stream()), "mv_head_product")
+    account(w.numel() * w.element_size() + N * nh * (n_in * 4 + n_out * y.element_size()), 2 * N * nh * n_in * n_out)
+    return y
+
+
+def latent_attention(qa: torch.Tensor, pool: torch.Tensor, page_size: int, page_table, positions, seq_of,
+                     out: torch.Tensor, nh: int, rank: int, rot: int, scale: float, *, window: int = 0,
+                     sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal softmax attention of every token of the step over its sequence's cached rows [rank + rot] (which already
+    hold the step's own): all heads read the same rows as keys, and the rows' first ``rank`` numbers as values.
+    ``qa`` float32 [N, nh, rank + rot], ``out`` float32 [N, nh, rank].  ``window`` w > 0: query i reads key j if
+    0 <= i - j < w.  ``sinks`` [nh]: exp(sink) joins each head's denominator.  Scores and softmax are float32."""
+    N = qa.shape[0]
+    if not 1 <= rank <= LATENT_MAX_RANK or rot < 0:
+        raise KernelError(f"latent_attention: rank {rank} must lie in 1..{LATENT_MAX_RANK}")
+    _check_latent_pool(pool, page_size, rank + rot, "latent_attention")
+    _guard("core", "latent_attention", qa.device, n_pages=pool.shape[0])
+    _check(_fn("core", "mv_latent_attention")(
+        _need(qa, "absorbed q", torch.float32, (N, nh, rank + rot)), pool.data_ptr(), pool.stride(0), _dt(pool),
+        _need(page_table, "page table", torch.int32), page_table.shape[1], int(page_size),
+        _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
+        _need(sinks, "sinks", torch.float32, (nh,), True), _need(out, "attention out", torch.float32, (N, nh, rank)),
+        N, nh, rank, rot, float(scale), int(window), _stream()), "mv_latent_attention")
+    return out
+
+
+def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, a: torch.Tensor,
+               dt_bias: torch.Tensor, a_log: torch.Tensor, state: torch.Tensor, slots, cu, out: torch.Tensor,
+               n_seqs: int, n_heads: int, kv_heads: int, dk: int, dv: int, *, q_scale: float,
+               norm_eps: float = 1e-6) -> torch.Tensor:
+    """The gated delta rule with a decay per key channel, token by token: per head S <- diag(g) S;
+    u = sigmoid(beta) (v - S^T k); S <- S + k u^T; o = S^T q, with q and k made unit vectors per head first
+    (x / sqrt(sum x^2 + norm_eps), q also times ``q_scale``) and g = exp(-exp(a_log_h) softplus(a + dt_bias)).
+    q, k [N, kv_heads * dk] (head h reads head h // (n_heads / kv_heads)), v [N, n_heads * dv], beta [N, n_heads],
+    a [N, n_heads * dk]: float32, column slices are fine; ``state`` float32 [slots, n_heads, dv, dk]; ``out``
+    float32 [N, n_heads * dv]."""
+    N = out.shape[0]
+    if not 1 <= dk <= MAX_SCAN_KEY_DIM or kv_heads < 1 or n_heads % kv_heads:
+        raise KernelError(f"delta_scan: key size {dk} (1..{MAX_SCAN_KEY_DIM}), {n_heads} heads on {kv_heads} kv heads")
+    qp, ldq = _cols(q, "delta_scan q", N, kv_heads * dk)
+    kp, ldk = _cols(k, "delta_scan k", N, kv_heads * dk)
+    vp, ldv = _cols(v, "delta_scan v", N, n_heads * dv)
+    bp, ldb = _cols(beta, "delta_scan beta", N, n_heads)
+    ap, lda = _cols(a, "delta_scan decay", N, n_heads * dk)
+    _guard("core", "delta_rule", out.device, n_slots=state.shape[0])
+    _check(_fn("core", "mv_delta_scan")(
+        qp, ldq, kp, ldk, vp, ldv, bp, ldb, ap, lda, _need(dt_bias, "dt_bias", torch.float32, (n_heads * dk,)),
+        _need(a_log, "A_log", torch.float32, (n_heads,)), float(q_scale), float(norm_eps),
+        _need(state, "delta_scan state", torch.float32, (None, n_heads, dv, dk)), _need(slots, "slots", torch.int32),
+        _need(cu, "cu", torch.int32), _need(out, "delta_scan out", torch.float32, (N, n_heads * dv)), int(n_seqs), n_heads,
+        kv_heads, dk, dv, _stream()), "mv_delta_scan")
+    account(2 * n_seqs * n_heads * dv * dk * 4 + N * (2 * kv_heads * dk + n_heads * (2 * dv + dk + 1)) * 4,
+            6 * N * n_heads * dk * dv)
     return out
 
 

@@ -136,7 +136,7 @@ class PreNormOptionalBlock(Part):
                 self.ffn.forward(g, resid, step)
         if self.token_input is not None:
             nxt = after.mixer_norm if isinstance(after, PreNormOptionalBlock) and isinstance(after.mixer_norm, LayerNorm) \
-                and getattr(self.token_input, "takes_norm", False) else None
+                and not after.mixer_norm.has_bias and getattr(self.token_input, "takes_norm", False) else None
             with profile_stage("token_input " + getattr(self.token_input, "kind", "?")):
                 if nxt is not None:
                     # another buffer than "normed": this block's rows there are done with, the next block's
@@ -224,3 +224,61 @@ class PostNormBlock(Part):
                 self._add(branches, self.ffn_norm, resid, rounded if want else None)
         if narrow and isinstance(after, PostNormBlock):
             step.handed = ("stream", rounded)
+
+
+@register("block", "parallel_prenorm")
+class ParallelPreNormBlock(Part):
+    """x += mixer(h) + feed_forward(h) with h = norm(x): ONE norm whose output both sublayers read (the feed-forward
+    is optional).  The residual stream stays in float32; the normed activations are in the model's dtype.  Both
+    sublayers add their results into the stream themselves."""
+
+    nested_roles = {"norm": "norm", "mixer": "mixer", "ffn": "feed_forward"}
+
+    def __init__(self, norm, mixer, ffn=None):
+        self.norm, self.mixer, self.ffn = norm, mixer, ffn
+
+    def nested(self):
+        parts = {"norm": self.norm, "mixer": self.mixer, "ffn": self.ffn}
+        return {k: v for k, v in parts.items() if v is not None}
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, resid, step, view) -> None:
+        N, H = resid.shape
+        u = self.scratch(step, "normed", (N, H), step.dtype)
+        with profile_stage("norm"):
+            self.norm.forward(resid, u)
+        with profile_stage("mixer " + getattr(self.mixer, "kind", "?")):
+            self.mixer.forward(u, resid, step, view)
+        if self.ffn is not None:
+            with profile_stage("feed_forward " + getattr(self.ffn, "kind", "?")):
+                self.ffn.forward(u, resid, step)
+
+
+@register("block", "stream_restart")
+class StreamRestart(Part):
+    """What stands before a pass over a run of layers that is walked several times with the same weights:
+    x += embedding output (with ``add_embedding``: every pass but the first) + steps[row], one learned vector a pass.
+    The embedding leaves its output for this through ``step.embedding_output``.  No mixer, no cache."""
+
+    def __init__(self, hidden: int, n_rows: int, row: int, add_embedding: bool):
+        if not 0 <= int(row) < int(n_rows):
+            raise ValueError(f"pass {row} of {n_rows}")
+        self.hidden, self.n_rows, self.row, self.add_embedding = int(hidden), int(n_rows), int(row), bool(add_embedding)
+
+    def param_specs(self):
+        from .spec import ParamSpec
+        return {"steps": ParamSpec((self.n_rows, self.hidden), "vector", "bias")}
+
+    def load(self, t) -> None:
+        self.vec = t["steps"][self.row].contiguous()
+
+    def forward(self, resid, step, view) -> None:
+        rows = None
+        if self.add_embedding:
+            rows = getattr(step, "embedding_output", None)
+            if rows is None:
+                raise RuntimeError("the embedding of this model does not keep its output for later passes")
+        with profile_stage("restart"):
+            K.add_rows_vector(resid, rows, self.vec)

@@ -5,6 +5,7 @@ from typing import Dict, Optional
 
 import torch
 
+from ..cache.needs import StateNeed
 from ..ops import kernels as K
 from ..ops.linear import linear, norm_link_ok
 from .base import Part
@@ -66,6 +67,40 @@ class ScaledEmbeddingWithPositions(Part):
                                 f"{self.positions.shape[0]} rows")
         K.embed_scaled_pos(self.weight, step.tokens, self.scale, self.positions, step.positions, x, rounded)
         step.handed = ("stream", rounded) if rounded is not None else None
+        return x
+
+
+@register("embedding", "table_bigram")
+class BigramEmbedding(Part):
+    """x_t = E[token_t] + B[r_t]: a token embedding plus a row of a hashed bigram table,
+    r_t = (token_(t-1) * mul_prev + token_t * mul_cur) mod buckets, and row ``buckets`` (the table's last) for a
+    sequence's first token.  The previous token is part of a sequence's state: one int32 per slot.  With ``keep``
+    a second copy of the rows is left in ``step.embedding_output`` for parts that add it to the stream again later."""
+
+    def __init__(self, vocab: int, hidden: int, buckets: int, mul_prev: int, mul_cur: int, keep: bool = False):
+        if buckets < 1:
+            raise ValueError(f"a bigram table needs at least one bucket, got {buckets}")
+        self.vocab, self.hidden, self.buckets = int(vocab), int(hidden), int(buckets)
+        self.mul_prev, self.mul_cur, self.keep = int(mul_prev), int(mul_cur), bool(keep)
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"weight": ParamSpec((self.vocab, self.hidden)), "bigram": ParamSpec((self.buckets + 1, self.hidden))}
+
+    def load(self, t) -> None:
+        self.weight, self.bigram = t["weight"], t["bigram"]
+        if self.bigram.dtype != self.weight.dtype:
+            self.weight, self.bigram = self.weight.float(), self.bigram.float()
+
+    def cache_need(self):
+        return StateNeed((1,), torch.int32)
+
+    def forward(self, step, view) -> torch.Tensor:
+        N = step.n_tokens
+        x = step.ws.get("resid", (N, self.hidden), torch.float32)
+        kept = step.ws.get("embedding_output", (N, self.hidden), torch.float32) if self.keep else None
+        K.embed_bigram(self.weight, self.bigram, step.tokens, step.positions, step.seq_of, step.cu, step.slots,
+                       view.state.view(-1), x, kept, self.mul_prev, self.mul_cur)
+        step.embedding_output = kept
         return x
 
 

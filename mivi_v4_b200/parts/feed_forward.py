@@ -91,8 +91,12 @@ class ClampedGLU(Part):
 
 @register("feed_forward", "routed_experts")
 class RoutedExperts(Part):
-    """Mixture of experts with sigmoid scores: every expert is W_down (silu(W_gate h) * (W_up h)) without
-    biases; router logits z = W_router h in float32, scores s = sigmoid(z); the experts form ``n_groups`` equal
+    """Mixture of experts: every expert is W_down (silu(W_gate h) * (W_up h)) without
+    biases; router logits z = W_router h in float32, scores s = sigmoid(z), or with ``score`` "softmax" softmax(z)
+    over all routed entries; with ``correction`` a learned number per entry is added to the scores for the CHOICE
+    only (the weights use the scores themselves); the weights are multiplied by ``out_scale``; the last
+    ``n_identity`` routed entries (after the ``n_experts`` experts with matrices) are identity experts whose output
+    is the input itself times the weight.  The entries form ``n_groups`` equal
     groups of neighbours, a group's score is the sum of its two largest scores, and only experts of the
     ``keep_groups`` best groups can be chosen; the ``top`` largest scores among them are chosen and weigh their
     experts by s / (sum of the chosen s + 1e-20).  With ``shared_ff`` > 0 a shared expert of that width runs for
@@ -107,19 +111,29 @@ class RoutedExperts(Part):
 
     overwrites = True
 
+    SCORES = {"sigmoid": K.ROUTE_SIGMOID, "softmax": K.ROUTE_SOFTMAX}
+
     def __init__(self, hidden: int, n_experts: int, ff: int, top: int, n_groups: int = 1, keep_groups: int = 1,
-                 shared_ff: int = 0):
-        if n_experts < 1 or n_experts > K.MAX_EXPERTS or n_groups < 1 or n_experts % n_groups:
-            raise ValueError(f"{n_experts} experts do not form {n_groups} equal groups (at most {K.MAX_EXPERTS} experts)")
-        if not 1 <= keep_groups <= n_groups or not 1 <= top <= min(32, keep_groups * (n_experts // n_groups)):
+                 shared_ff: int = 0, score: str = "sigmoid", correction: bool = False, out_scale: float = 1.0,
+                 n_identity: int = 0):
+        routed = int(n_experts) + int(n_identity)
+        if n_experts < 1 or n_identity < 0 or routed > K.MAX_EXPERTS or n_groups < 1 or routed % n_groups:
+            raise ValueError(f"{routed} routed entries do not form {n_groups} equal groups (at most {K.MAX_EXPERTS})")
+        if not 1 <= keep_groups <= n_groups or not 1 <= top <= min(32, keep_groups * (routed // n_groups)):
             raise ValueError(f"{top} experts cannot be chosen from {keep_groups} of {n_groups} groups of "
-                             f"{n_experts // n_groups} (at most 32)")
+                             f"{routed // n_groups} (at most 32)")
+        if score not in self.SCORES:
+            raise ValueError(f"router score {score!r}; known: {', '.join(sorted(self.SCORES))}")
         self.hidden, self.E, self.ff, self.top = int(hidden), int(n_experts), int(ff), int(top)
         self.n_groups, self.keep, self.shared_ff = int(n_groups), int(keep_groups), int(shared_ff)
+        self.score, self.has_correction, self.out_scale = score, bool(correction), float(out_scale)
+        self.I, self.routed = int(n_identity), routed
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         H, F = self.hidden, self.ff
-        specs = {"router": ParamSpec((self.E, H))}
+        specs = {"router": ParamSpec((self.routed, H))}
+        if self.has_correction:
+            specs["correction"] = ParamSpec((self.routed,), "vector", "bias")
         for e in range(self.E):
             specs.update({f"e{e}.gate": ParamSpec((F, H)), f"e{e}.up": ParamSpec((F, H)), f"e{e}.down": ParamSpec((H, F))})
         if self.shared_ff:
@@ -131,7 +145,7 @@ class RoutedExperts(Part):
     def active_matrix_elements(self) -> int:
         """Matrix elements that one token is multiplied with: the router, its chosen experts, the shared one."""
         H = self.hidden
-        return self.E * H + 3 * self.top * self.ff * H + (3 * self.shared_ff * H + H if self.shared_ff else 0)
+        return self.routed * H + 3 * self.top * self.ff * H + (3 * self.shared_ff * H + H if self.shared_ff else 0)
 
     def load(self, t) -> None:
         names = [f"e{e}." for e in range(self.E)] + (["shared."] if self.shared_ff else [])
@@ -157,6 +171,7 @@ class RoutedExperts(Part):
         if pad:
             rows.append(torch.zeros((pad, self.hidden), dtype=rows[0].dtype, device=rows[0].device))
         self.w_router = torch.cat(rows, dim=0).contiguous()
+        self.correction = t.get("correction")
         # the shared expert's down matrix by itself, for the steps that sort the tokens by expert (kept in a list,
         # beside the weights that every step reads: a copy of columns that those steps read from it instead)
         self._shared_down = [self.w_down[:, self.E * self.ff:].contiguous()] if self.shared_ff else []
@@ -176,19 +191,21 @@ class RoutedExperts(Part):
 
     def _sorted_ok(self, g, step, N: int) -> bool:
         return (N * self.top >= self.SORTED_ROWS_AN_EXPERT * self.E and not step.is_decode and self.top < self.E
-                and self.group == K.SWIGLU_GROUP and self.ff % 8 == 0 and g.shape[1] % 8 == 0
+                and self.I == 0 and self.group == K.SWIGLU_GROUP and self.ff % 8 == 0 and g.shape[1] % 8 == 0
                 and tensor_core_ok(g, self.w_gu) and self.w_down.dtype == torch.bfloat16)
 
     def forward(self, g, resid, step, accumulate: bool = True) -> None:
         N = g.shape[0]
-        E, F = self.E, self.E * self.ff + self.shared_ff
-        cols = E + (1 if self.shared_ff else 0)
+        E, F, I = self.E, self.E * self.ff + self.shared_ff, self.I
+        sg = 1 if self.shared_ff else 0
+        cols = self.routed + sg                  # a dense row: [experts | the shared gate | identity experts]
         z = self.scratch(step, "z", (N, self.w_router.shape[0]), torch.float32)
         linear(g, self.w_router, z)
         dense = self.scratch(step, "route", (N, cols), torch.float32)
         pick = self.scratch(step, "pick", (N, self.top), torch.int32)
         pick_w = self.scratch(step, "pick_w", (N, self.top), torch.float32)
-        K.route(z[:, :cols], dense, pick, pick_w, E, self.n_groups, self.keep, self.top, bool(self.shared_ff))
+        K.route(z[:, :cols], dense, pick, pick_w, self.routed, self.n_groups, self.keep, self.top, bool(self.shared_ff),
+                mode=self.SCORES[self.score], correction=self.correction, out_scale=self.out_scale, n_identity=I)
         if self._sorted_ok(g, step, N):
             return self._forward_sorted(g, resid, step, accumulate, dense, pick, pick_w)
         h = self.scratch(step, "ffh", (N, F), step.dtype)
@@ -196,12 +213,14 @@ class RoutedExperts(Part):
                 and tensor_core_ok(g, self.w_gu)):
             # long steps: gate and up never reach memory; the weights go on the rounded activations
             linear_swiglu(g, self.w_gu, h)
-            K.scale_expert_columns(h, dense, E, self.ff, self.shared_ff)
+            K.scale_expert_columns(h, dense, E, self.ff, self.shared_ff, extra_cols=I)
         else:
             gu = self.scratch(step, "proj", (N, 2 * F), torch.float32)
             linear(g, self.w_gu, gu)
-            K.routed_glu(gu, dense, h, E, self.ff, self.shared_ff, self.group, self.shared_group)
+            K.routed_glu(gu, dense, h, E, self.ff, self.shared_ff, self.group, self.shared_group, extra_cols=I)
         linear(h, self.w_down, resid, accumulate=accumulate)
+        if I:
+            K.identity_experts(g, dense, E + sg, I, resid)
 
     def _forward_sorted(self, g, resid, step, accumulate, dense, pick, pick_w) -> None:
         N, H = g.shape

@@ -587,3 +587,178 @@ class ParallelMixers(Part):
             resid.add_(yl, alpha=sl).add_(yr, alpha=sr)
         else:
             torch.add(yl * sl, yr, alpha=sr, out=resid)
+
+
+@register("mixer", "latent_attention")
+class LatentAttention(Part):
+    """Softmax attention over a compressed cache (the multi-head latent attention of DeepSeek-V2): per head q = W_q h
+    is [``dim`` unrotated | ``rot_dim`` rotated]; W_dkv h gives ``kv_rank`` numbers, divided by their root mean
+    square and multiplied by a weight (the latent c), and ``rot_dim`` more, one rotated key part r shared by all
+    heads; per head the unrotated key is W_uk c and the value W_uv c; score = (q_unrotated . k_unrotated +
+    q_rotated . r) * scale; a sliding ``window`` (0: none); with ``sink`` a learned number per head joins the softmax's
+    denominator; with ``gated`` the concatenated heads are multiplied by sigmoid(W_g h); then W_o.  The position
+    part turns the first ``position.head_dim`` of the ``rot_dim`` elements, element i with i + head_dim / 2.
+
+    Only [c | r] is cached, one row a token for all heads.  W_uk is folded into the query
+    (qa = [W_uk^T q_unrotated | q_rotated]) and W_uv applied to the weighted sum of the cached c, so keys and values
+    are never rebuilt.  Scores, softmax, norm and angles are float32."""
+
+    nested_roles = {"position": "position"}
+    overwrites = True
+
+    def __init__(self, hidden: int, n_heads: int, dim: int, rot_dim: int, value_dim: int, kv_rank: int, scale: float,
+                 eps: float, position, window: int = 0, sink: bool = True, gated: bool = True):
+        if not 1 <= kv_rank <= K.LATENT_MAX_RANK or not 0 <= rot_dim <= K.LATENT_MAX_ROT:
+            raise ValueError(f"latent size {kv_rank} (1..{K.LATENT_MAX_RANK}), rotated size {rot_dim} (0..{K.LATENT_MAX_ROT})")
+        self.hidden, self.nh, self.dim, self.rd = int(hidden), int(n_heads), int(dim), int(rot_dim)
+        self.dv, self.rank, self.scale, self.eps = int(value_dim), int(kv_rank), float(scale), float(eps)
+        self.window, self.sink, self.gated, self.position = int(window), bool(sink), bool(gated), position
+        self.rot_dims = 0
+        if isinstance(position, Rope):
+            if position.style != "half_split" or position.head_dim > self.rd:
+                raise ValueError("the rotation pairs element i with i + dims / 2 over at most the rotated size")
+            self.rot_dims = position.head_dim
+        elif position.rotary("cpu") is not None:
+            raise ValueError("a rotation that is not a Rope part cannot say how many elements it turns")
+
+    def nested(self):
+        return {"position": self.position}
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        H, nh, qd, dv, rank = self.hidden, self.nh, self.dim + self.rd, self.dv, self.rank
+        specs = {"q": ParamSpec((nh * qd, H)), "dkv": ParamSpec((rank + self.rd, H)),
+                 "dkv.norm": ParamSpec((rank,), "vector", "norm"), "uk": ParamSpec((nh * self.dim, rank)),
+                 "uv": ParamSpec((nh * dv, rank)), "o": ParamSpec((H, nh * dv))}
+        if self.sink:
+            specs["sink"] = ParamSpec((nh,), "vector", "bias")
+        if self.gated:
+            specs["g"] = ParamSpec((nh * dv, H))
+        return specs
+
+    def load(self, t) -> None:
+        self.w_in = _fuse_rows([t["q"], t["dkv"]] + ([t["g"]] if self.gated else []))
+        self.c_norm, self.sinks, self.w_o = t["dkv.norm"], t.get("sink"), t["o"]
+        self.w_uk, self.w_uv = t["uk"].contiguous(), t["uv"].contiguous()
+
+    def cache_need(self):
+        return KVNeed(1, self.rank + self.rd, self.window, self.rank, values_in_keys=True)
+
+    def forward(self, u, resid, step, view, accumulate: bool = True) -> None:
+        N = u.shape[0]
+        nh, dim, rd, dv, rank = self.nh, self.dim, self.rd, self.dv, self.rank
+        c0 = nh * (dim + rd)
+        g0 = c0 + rank + rd
+        proj = self.scratch(step, "proj", (N, self.w_in.shape[0]), torch.float32)
+        linear(u, self.w_in, proj)
+        rot = self.position.rotary(u.device) if self.rot_dims else None
+        qa = self.scratch(step, "qa", (N, nh, rank + rd), torch.float32)
+        K.latent_prepare(proj, 0, c0, self.c_norm, self.eps, rot[0] if rot is not None else None, step.positions,
+                         step.seq_of, view.page_table, view.pool, view.page_size, qa, nh, dim, rd, rank, self.rot_dims)
+        K.head_product(proj[:, :c0].unflatten(1, (nh, dim + rd)), self.w_uk, qa, nh, dim, rank, transposed=True)
+        o_lat = self.scratch(step, "o_lat", (N, nh, rank), torch.float32)
+        K.latent_attention(qa, view.pool, view.page_size, view.page_table, step.positions, step.seq_of, o_lat, nh, rank,
+                           rd, self.scale, window=self.window, sinks=self.sinks)
+        if K.profiling_on():
+            reach = self.window or None
+            pairs = sum(sum(min(s + i + 1, reach) if reach else s + i + 1 for i in range(n))
+                        for s, n in zip(step.host_starts, step.host_lens))
+            K.account((rank + rd) * view.pool.element_size() * pairs + N * nh * (2 * rank + rd) * 4,
+                      2 * nh * (2 * rank + rd) * pairs)
+        y = self.scratch(step, "mix", (N, nh * dv), step.dtype)
+        K.head_product(o_lat, self.w_uv, y.view(N, nh, dv), nh, rank, dv,
+                       gate=proj[:, g0:g0 + nh * dv] if self.gated else None)
+        linear(y, self.w_o, resid, accumulate=accumulate)
+
+
+def _block_diagonal(a: torch.Tensor, b: torch.Tensor, cols: int, multiple: int = 16) -> torch.Tensor:
+    """[[a, 0], [0, b]] with ``cols`` columns (>= the two widths together) and rows padded to ``multiple``: two
+    products of different inputs as one product of the inputs side by side."""
+    if a.dtype != b.dtype:
+        a, b = a.float(), b.float()
+    rows = a.shape[0] + b.shape[0]
+    out = torch.zeros((rows + (-rows % multiple), cols), dtype=a.dtype, device=a.device)
+    out[:a.shape[0], :a.shape[1]] = a
+    out[a.shape[0]:rows, a.shape[1]:a.shape[1] + b.shape[1]] = b
+    return out.contiguous()
+
+
+@register("mixer", "channel_delta")
+class ChannelDelta(Part):
+    """The gated delta rule with a decay per key channel (Yang, Kautz and Hatamizadeh, "Gated Delta Networks:
+    Improving Mamba2 with Delta Rule", with the decay of one number a head widened to one a key channel):
+    q = W_q h and k = W_k h on ``kv_heads`` heads of ``key_dim``, v = W_v h on ``n_heads`` heads of ``value_dim``
+    (head h reads q/k head h // (n_heads / kv_heads)); each passes a causal convolution of ``conv`` taps per
+    channel (no bias, the last tap the current token's) and silu; q and k become unit vectors per head
+    (x / sqrt(sum x^2 + 1e-6)), q times key_dim^-1/2; beta = sigmoid(W_b h) per head;
+    g = exp(-exp(A_log_h) softplus(W_a2 (W_a1 h) + dt_bias)) per head and key channel; per head
+    S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; each head's o over its root mean square, times
+    ``norm`` [value_dim], times sigmoid(W_g2 (W_g1 h)); then W_o.  The state [heads, value_dim, key_dim] and the
+    convolution's last conv - 1 inputs are float32 per sequence and start at zero; decays, gates of the recurrence,
+    unit norms, state and sums are float32 in every run.  ``decay_rank`` / ``gate_rank``: the inner sizes of the
+    two-step projections; None takes them from the checkpoint."""
+
+    overwrites = True
+    UNIT_EPS = 1e-6
+
+    def __init__(self, hidden: int, n_heads: int, kv_heads: int, key_dim: int, value_dim: int, conv: int, eps: float,
+                 decay_rank: Optional[int] = None, gate_rank: Optional[int] = None):
+        if kv_heads < 1 or n_heads % kv_heads:
+            raise ValueError(f"{n_heads} heads are not a multiple of {kv_heads} kv heads")
+        if not 1 <= key_dim <= K.MAX_SCAN_KEY_DIM:
+            raise ValueError(f"key size {key_dim} is outside 1..{K.MAX_SCAN_KEY_DIM}")
+        if not 1 <= conv <= K.MAX_CONV_K:
+            raise ValueError(f"convolution width {conv} is outside 1..{K.MAX_CONV_K}")
+        self.hidden, self.nh, self.nkv, self.dk, self.dv = int(hidden), int(n_heads), int(kv_heads), int(key_dim), int(value_dim)
+        self.conv, self.eps = int(conv), float(eps)
+        self.decay_rank = None if decay_rank is None else int(decay_rank)
+        self.gate_rank = None if gate_rank is None else int(gate_rank)
+        self.channels = 2 * self.nkv * self.dk + self.nh * self.dv
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        H, qk, vv, hk, c = self.hidden, self.nkv * self.dk, self.nh * self.dv, self.nh * self.dk, self.conv
+        return {"q": ParamSpec((qk, H)), "q.conv": ParamSpec((qk, c), "vector", "conv"),
+                "k": ParamSpec((qk, H)), "k.conv": ParamSpec((qk, c), "vector", "conv"),
+                "v": ParamSpec((vv, H)), "v.conv": ParamSpec((vv, c), "vector", "conv"),
+                "b": ParamSpec((self.nh, H)), "A_log": ParamSpec((self.nh,), "vector", "bias"),
+                "norm": ParamSpec((self.dv,), "vector", "norm"),
+                "a1": ParamSpec((self.decay_rank, H)), "a2": ParamSpec((hk, self.decay_rank)),
+                "dt_bias": ParamSpec((hk,), "vector", "bias"),
+                "g1": ParamSpec((self.gate_rank, H)), "g2": ParamSpec((vv, self.gate_rank)), "o": ParamSpec((H, vv))}
+
+    def load(self, t) -> None:
+        for one, two in (("a1", "a2"), ("g1", "g2")):
+            if t[one].shape[0] != t[two].shape[1]:
+                raise ValueError(f"the two projections disagree: {one} is {tuple(t[one].shape)}, {two} {tuple(t[two].shape)}")
+        self.w_in = _fuse_rows([t["q"], t["k"], t["v"], t["b"]])
+        self.w_low = _fuse_rows([t["a1"], t["g1"]])
+        self.w_up = _block_diagonal(t["a2"], t["g2"], self.w_low.shape[0])
+        self.taps = torch.cat([t["q.conv"], t["k.conv"], t["v.conv"]], dim=0).contiguous()
+        self.a_log, self.dt_bias, self.norm, self.w_o = t["A_log"], t["dt_bias"], t["norm"], t["o"]
+
+    def cache_need(self):
+        needs = [StateNeed((self.nh, self.dv, self.dk))]
+        if self.conv > 1:
+            needs.append(StateNeed((self.conv - 1, self.channels)))
+        return needs
+
+    def forward(self, u, resid, step, view, accumulate: bool = True) -> None:
+        N = u.shape[0]
+        nh, nkv, dk, dv, C = self.nh, self.nkv, self.dk, self.dv, self.channels
+        qk, vv, hk = nkv * dk, nh * dv, nh * dk
+        memory = view[0]
+        conv_state = view[1].state if self.conv > 1 else None
+        proj = self.scratch(step, "proj", (N, self.w_in.shape[0]), torch.float32)
+        linear(u, self.w_in, proj)
+        low = self.scratch(step, "low", (N, self.w_low.shape[0]), step.dtype)
+        linear(u, self.w_low, low)
+        up = self.scratch(step, "up", (N, self.w_up.shape[0]), torch.float32)
+        linear(low, self.w_up, up)
+        xbc = self.scratch(step, "xbc", (N, C), torch.float32)
+        K.causal_conv_silu(proj[:, :C], self.taps, None, conv_state, step.seq_of, step.cu, step.slots, xbc, step.n_seqs)
+        o = self.scratch(step, "o", (N, vv), torch.float32)
+        K.delta_scan(xbc[:, :qk], xbc[:, qk:2 * qk], xbc[:, 2 * qk:], proj[:, C:C + nh], up[:, :hk], self.dt_bias,
+                     self.a_log, memory.state, step.slots, step.cu, o, step.n_seqs, nh, nkv, dk, dv,
+                     q_scale=dk ** -0.5, norm_eps=self.UNIT_EPS)
+        y = self.scratch(step, "mix", (N, vv), step.dtype)
+        K.gated_rmsnorm(o, up[:, hk:hk + vv], self.norm, dv, self.eps, K.GATE_SIGMOID, y)
+        linear(y, self.w_o, resid, accumulate=accumulate)

@@ -37,15 +37,20 @@ class RMSNorm(Part):
 
 @register("norm", "layernorm")
 class LayerNorm(Part):
-    """y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * weight over the last dimension, no bias, in
-    float32.  It is not carried by the products around it (it has no ``link``): it always runs as a kernel."""
+    """y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * weight (+ bias, with ``bias``) over the last
+    dimension, in float32.  It is not carried by the products around it (it has no ``link``): it always runs as
+    a kernel."""
 
-    def __init__(self, dim: int, eps: float):
-        self.dim, self.eps = int(dim), float(eps)
+    def __init__(self, dim: int, eps: float, bias: bool = False):
+        self.dim, self.eps, self.has_bias = int(dim), float(eps), bool(bias)
         self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.dim,), "vector", "norm")}
+        specs = {"weight": ParamSpec((self.dim,), "vector", "norm")}
+        if self.has_bias:
+            specs["bias"] = ParamSpec((self.dim,), "vector", "bias")
+        return specs
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-        return K.layernorm(x, self.weight, self.eps, out, rows)
+        return K.layernorm(x, self.weight, self.eps, out, rows, bias=self.bias)
