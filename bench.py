@@ -9,6 +9,7 @@ prefill, then generation timed without its first token).
     python bench.py --stages decode|prefill [--batch B] (where a step's time goes, by stage and kernel)
     python bench.py --design votavik [--stages ..]      (the Votavik decoder beside the LFM2 model of equal sizes)
     python bench.py --design tevirax [--stages ..]      (the Tevirax decoder beside the Votavik decoder of equal sizes)
+    python bench.py --design puzorax [--stages ..]      (the Puzorax decoder beside the Tevirax decoder of equal sizes)
     python bench.py --kernel NAME [--m .. --n .. --k ..] (one kernel alone, for timing and for profilers)
 
 One "step" is one decode step of the whole batch.  Prints ONE JSON line:
@@ -229,6 +230,23 @@ def tevirax_config(width, layers, heads, kv_heads, ff, vocab):
                         "mlp": {"kind": "dense", "ff": ff} if i == 0 else moe} for i in range(layers)]}
 
 
+def puzorax_config(width, layers, heads, kv_heads, ff, vocab):
+    """Two delta-rule layers, then a layer of latent attention, and so on; layers 3 to 5 run twice, so the model has
+    ``layers`` layer runs from ``layers`` - 3 layers' weights.  Every layer carries a mixture of 16 experts of an eighth
+    of the feed-forward width and 2 identity experts, 4 chosen."""
+    delta = {"heads": max(1, width // 128), "kv_heads": max(1, width // 256), "dim": 128, "vdim": 128, "conv": 4,
+             "decay_rank": 64, "gate_rank": 64}
+    latent = {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "scale": 96 ** -0.5,
+              "mask": {"size": 1024}, "rot": {"dims": 32, "base": 1000000.0}}
+    moe = {"kind": "moe", "expert": {"ff": ff // 8}, "router": {"experts": 16, "identity": 2, "top": 4, "scale": 2.5}}
+    n = max(6, layers - 3)
+    return {"architecture": "Puzorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+            "loop": {"start": 3, "stop": 6, "times": 2},
+            "layers": [{"type": "latent_attention" if i % 3 == 2 else "channel_delta",
+                        "mixer": latent if i % 3 == 2 else delta, "mlp": moe} for i in range(n)]}
+
+
 def lfm2_like(width, layers, heads, kv_heads, ff, vocab):
     cfg = dict(BENCH_CONFIG)
     cfg.update(hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv_heads,
@@ -239,14 +257,15 @@ def lfm2_like(width, layers, heads, kv_heads, ff, vocab):
 
 def run_design(args, warmup: int) -> int:
     """Prefill and decode throughput of a further design (--design) at the sizes of DESIGN_SIZES, each beside its
-    closest neighbour in the library at equal sizes (Votavik beside LFM2, Tevirax beside Votavik), random weights,
+    closest neighbour in the library at equal sizes (Votavik beside LFM2, Tevirax beside Votavik, Puzorax beside Tevirax), random weights,
     bfloat16: one JSON line.  With --stages: where a step of the design's model (--size) goes, kernel by kernel."""
     import torch
     from mivi_v4_b200 import measure, random_model
     pk, pk_src = peaks()
     # the design that was asked for, beside its closest neighbour in the library at equal sizes
-    design_cfg = {"votavik": votavik_config, "tevirax": tevirax_config}[args.design]
-    beside, beside_cfg = {"votavik": ("lfm2", lfm2_like), "tevirax": ("votavik", votavik_config)}[args.design]
+    design_cfg = {"votavik": votavik_config, "tevirax": tevirax_config, "puzorax": puzorax_config}[args.design]
+    beside, beside_cfg = {"votavik": ("lfm2", lfm2_like), "tevirax": ("votavik", votavik_config),
+                          "puzorax": ("tevirax", tevirax_config)}[args.design]
     if args.stages:
         model = random_model(design_cfg(*DESIGN_SIZES[args.size]), seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
         lens = [args.tokens] if args.stages == "prefill" else [args.prompt_len] * args.batch
@@ -367,7 +386,7 @@ def main() -> int:
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="run one of the two further workloads instead of the default benchmark")
     ap.add_argument("--size", default="w2048", choices=sorted(DESIGN_SIZES), help="with --design --stages: which size")
-    ap.add_argument("--design", default=None, choices=["votavik", "tevirax"],
+    ap.add_argument("--design", default=None, choices=["votavik", "tevirax", "puzorax"],
                     help="measure a further design beside its closest neighbour in the library at equal sizes (Votavik beside LFM2, "
                          "Tevirax beside Votavik) instead of the default benchmark")
     ap.add_argument("--stages", default=None, choices=["decode", "prefill"],

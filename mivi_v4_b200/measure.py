@@ -55,6 +55,10 @@ def model_numbers(model) -> dict:
             return 5 * m.nh * m.state * m.dv * T
         if hasattr(m, "hd") and hasattr(m, "nh"):                      # softmax attention, every earlier key
             return 4 * m.nh * m.hd * T * (T + 1) // 2
+        if hasattr(m, "rank") and hasattr(m, "rd"):                    # softmax attention over a compressed cache, a window
+            reach = m.window if m.window else T
+            pairs = T * (T + 1) // 2 if reach >= T else reach * (reach + 1) // 2 + (T - reach) * reach
+            return 2 * m.nh * (m.dim + m.rd + m.dv) * pairs
         if hasattr(m, "window") and hasattr(m, "dk"):                 # softmax attention, a window and kept first tokens
             reach = m.window + m.keep_first if m.window else T
             pairs = T * (T + 1) // 2 if reach >= T else reach * (reach + 1) // 2 + (T - reach) * reach

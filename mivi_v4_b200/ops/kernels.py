@@ -625,7 +625,8 @@ def causal_conv_silu(u: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.T
     if not 1 <= K <= MAX_CONV_K:
         raise KernelError(f"causal_conv_silu: {K} taps are outside 1..{MAX_CONV_K}")
     up, ldu = _cols(u, "causal_conv_silu input", N, C)
-    _guard("core", "state_space", out.device, n_slots=state.shape[0])
+    if K > 1:
+        _guard("core", "state_space", out.device, n_slots=state.shape[0])
     _check(_fn("core", "mv_causal_conv_silu")(
         up, ldu, _need(taps, "conv taps", torch.float32, (C, K)), _need(bias, "conv bias", torch.float32, (C,), True),
         _need(state, "conv state", torch.float32, (None, max(K - 1, 0), C)) if K > 1 else None,

@@ -77,8 +77,9 @@ def latent_attention(h, p: Dict[str, torch.Tensor], m: dict, eps: float, rnd: Ro
     q = _lin(h, p["q"], rnd).view(T, H, dim + rd)
     dkv = _lin(h, p["dkv"], rnd)
     c = rms_norm(dkv[:, :rank], p["dkv.norm"], eps)
-    k_rot = rotate_half(dkv[:, rank:], pos, m["rot"]["base"], m["rot"]["dims"])          # [T, rd], one for all heads
-    q_rot = rotate_half(q[..., dim:], pos, m["rot"]["base"], m["rot"]["dims"])
+    rot = m.get("rot") or {"base": 1.0, "dims": 0}
+    k_rot = rotate_half(dkv[:, rank:], pos, rot["base"], rot["dims"])                    # [T, rd], one for all heads
+    q_rot = rotate_half(q[..., dim:], pos, rot["base"], rot["dims"])
     k_un = _lin(c, p["uk"], rnd).view(T, H, dim)
     v = _lin(c, p["uv"], rnd).view(T, H, vd)
     s = torch.einsum("thd,shd->hts", _r(q[..., :dim], rnd), _r(k_un, rnd)) + torch.einsum("thd,sd->hts", _r(q_rot, rnd), _r(k_rot, rnd))
@@ -144,20 +145,24 @@ def channel_delta(h, p: Dict[str, torch.Tensor], m: dict, eps: float, rnd: Round
 
 
 # ---- mixture of experts ----------------------------------------------------------------------------------------
-def route(z, correction, top, scale):
+def route(z, correction, top, scale, margins: Optional[list] = None):
     """z [T, E]: scores softmax(z); the ``top`` largest of score + correction are chosen; their weights are
-    the scores themselves over their sum, times ``scale``.  Returns a dense [T, E] matrix of weights."""
+    the scores themselves over their sum, times ``scale``.  Returns a dense [T, E] matrix of weights.
+    ``margins``: a list that gets, per token, how far the last chosen entry lies above the first one left out."""
     s = torch.softmax(z, dim=-1)
     pick = torch.topk(s + correction.to(F), top, dim=-1).indices
+    if margins is not None and top < s.shape[-1]:
+        ranked = torch.sort(s + correction.to(F), dim=-1, descending=True).values
+        margins.append(ranked[:, top - 1] - ranked[:, top])
     w = torch.gather(s, 1, pick)
     w = w / (w.sum(-1, keepdim=True) + 1e-20) * scale
     return torch.zeros_like(s).scatter(1, pick, w)
 
 
-def moe(h, p: Dict[str, torch.Tensor], mlp: dict, rnd: Round = None):
+def moe(h, p: Dict[str, torch.Tensor], mlp: dict, rnd: Round = None, margins: Optional[list] = None):
     r = mlp["router"]
     E, I = r["experts"], r.get("identity", 0)
-    dense = route(_lin(h, p["router"], rnd), p["correction"], r["top"], r["scale"])
+    dense = route(_lin(h, p["router"], rnd), p["correction"], r["top"], r["scale"], margins)
     y = torch.zeros_like(h)
     for e in range(E):
         a = _lin(h, p[f"e{e}.gate"], rnd)
@@ -173,7 +178,7 @@ def sub(tensors: Dict[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor
     return {k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def layer(x, i: int, tensors, cfg, rnd: Round = None):
+def layer(x, i: int, tensors, cfg, rnd: Round = None, margins: Optional[list] = None):
     L = cfg["layers"][i]
     eps = cfg["norm"]["eps"]
     h = layer_norm(x, tensors[f"l{i}.norm1"], tensors[f"l{i}.norm1.b"], eps)
@@ -185,7 +190,7 @@ def layer(x, i: int, tensors, cfg, rnd: Round = None):
     else:
         raise ValueError(L["type"])
     if L.get("mlp") is not None:
-        y = y + moe(h, sub(tensors, f"l{i}.mlp."), L["mlp"], rnd)
+        y = y + moe(h, sub(tensors, f"l{i}.mlp."), L["mlp"], rnd, margins)
     return x + y
 
 
@@ -202,9 +207,9 @@ def layer_runs(cfg) -> List[tuple]:
     return runs + [(i, None, False) for i in range(stop, n)]
 
 
-def forward(tokens, tensors, cfg, rnd: Round = None, keep_layers: bool = False):
+def forward(tokens, tensors, cfg, rnd: Round = None, keep_layers: bool = False, margins: Optional[list] = None):
     """Logits [T, vocab] of one sequence from its first token; with ``keep_layers`` also the stream after every
-    layer run."""
+    layer run; ``margins`` collects the routers' margins (see ``route``)."""
     x0 = embedding(tokens, tensors["embed"], tensors["bigram"], cfg)
     x = x0
     kept = []
@@ -213,9 +218,19 @@ def forward(tokens, tensors, cfg, rnd: Round = None, keep_layers: bool = False):
             if t > 0:
                 x = x + x0
             x = x + tensors["loop.step"].to(F)[t]
-        x = layer(x, i, tensors, cfg, rnd)
+        x = layer(x, i, tensors, cfg, rnd, margins)
         if keep_layers:
             kept.append(x)
     f = layer_norm(x, tensors["final.norm"], tensors["final.norm.b"], cfg["norm"]["eps"])
     logits = _lin(f, tensors["head"], rnd)
     return (logits, torch.stack(kept)) if keep_layers else logits
+
+
+def greedy(tokens, tensors, cfg, n_new: int) -> List[int]:
+    """``n_new`` tokens, each the largest logit after everything before it (the whole sequence is run again)."""
+    seq, out = list(tokens), []
+    for _ in range(n_new):
+        nxt = int(forward(seq, tensors, cfg)[-1].argmax())
+        seq.append(nxt)
+        out.append(nxt)
+    return out
