@@ -155,3 +155,228 @@ MV_API int mv_delta_scan(const float* q, int ldq, const float* k, int ldk, const
 #undef DR_LAUNCH
     return mv_launch_status();
 }
+
+// ------------------------------------------------------------------------------------------- steps of many tokens
+// Two kernels.  delta_prepare does, once per token, what does not depend on the state: q and k as unit vectors
+// (q also times q_scale), k . q of each q/k head, the decays g, and beta; one row of `prep` a token:
+//     [q: kv_heads dk | k: kv_heads dk | g: heads dk | beta: heads | k.q: kv_heads]      (row stride ldp, 32-bit)
+// delta_scan_long then walks a sequence with nothing but the recurrence in its loop.  The tokens come through
+// shared memory sixteen at a time, the next sixteen on their way (cp.async) while these are worked on.  In the
+// loop  S' = diag(g) S  is read twice at once, a = S'^T k and b = S'^T q, so that one round of shuffles serves
+// both; u = beta (v - a); o = b + u (k . q), which is (S' + k u^T)^T q; S = S' + k u^T.
+#define DL_CHUNK 16
+
+__global__ void __launch_bounds__(256)
+delta_prepare_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
+                     const float* __restrict__ b, int ldb, const float* __restrict__ a, int lda,
+                     const float* __restrict__ dt_bias, const float* __restrict__ a_log, float q_scale, float norm_eps,
+                     float* __restrict__ prep, int ldp, int n_heads, int kv_heads, int dk) {
+    mv_pdl_begin();
+    const int n = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    float* row = prep + (size_t)n * ldp;
+    const int qk = kv_heads * dk, hk = n_heads * dk;
+    for (int h = warp; h < kv_heads; h += nwarps) {
+        const float* qh = q + (size_t)n * ldq + (size_t)h * dk;
+        const float* kh = k + (size_t)n * ldk + (size_t)h * dk;
+        float sq = 0.f, sk = 0.f, dot = 0.f;
+        for (int i = lane; i < dk; i += 32) {
+            const float x = qh[i], y = kh[i];
+            sq = fmaf(x, x, sq);
+            sk = fmaf(y, y, sk);
+            dot = fmaf(x, y, dot);
+        }
+        sq = mv_warp_sum(sq);
+        sk = mv_warp_sum(sk);
+        dot = mv_warp_sum(dot);
+        const float fq = q_scale / sqrtf(sq + norm_eps), fk = 1.0f / sqrtf(sk + norm_eps);
+        for (int i = lane; i < dk; i += 32) {
+            row[(size_t)h * dk + i] = qh[i] * fq;
+            row[qk + (size_t)h * dk + i] = kh[i] * fk;
+        }
+        if (lane == 0) row[2 * qk + hk + n_heads + h] = dot * fq * fk;
+    }
+    for (int e = threadIdx.x; e < hk; e += blockDim.x) {
+        const int h = e / dk;
+        row[2 * qk + e] = expf(-expf(a_log[h]) * dr_softplus(a[(size_t)n * lda + e] + dt_bias[e]));
+    }
+    for (int h = threadIdx.x; h < n_heads; h += blockDim.x)
+        row[2 * qk + hk + h] = 1.0f / (1.0f + expf(-b[(size_t)n * ldb + h]));
+}
+
+__device__ __forceinline__ void dl_copy4(float* smem, const float* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void dl_copy16(float* smem, const float* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void dl_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void dl_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// One buffer of shared memory: [q: CHUNK dk | k: CHUNK dk | g: CHUNK dk | v: CHUNK DR_COLS | beta: CHUNK | k.q: CHUNK]
+template <int R>
+__global__ void __launch_bounds__(DR_COLS * DR_PART)
+delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __restrict__ v, int ldv,
+                       float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu,
+                       float* __restrict__ o, int n_heads, int kv_heads, int dk, int dv, int wide) {
+    mv_pdl_begin();
+    extern __shared__ __align__(16) float dl_smem[];
+    const int per = DL_CHUNK * (3 * dk + DR_COLS + 2);
+    const int tile = blockIdx.x, h = blockIdx.y, sq = blockIdx.z;
+    const int tid = threadIdx.x, p = tid & (DR_PART - 1), jl = tid >> 3;
+    const int j = tile * DR_COLS + jl;
+    const int row0 = cu[sq], len = cu[sq + 1] - row0;
+    if (len <= 0) return;
+    const int hk = h / (n_heads / kv_heads);
+    const int qk = kv_heads * dk;
+    const int slot = mv_read_slot(slots[sq]);
+    float* srow = state + (((size_t)slot * n_heads + h) * dv + (j < dv ? j : 0)) * dk;
+    float S[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int i = p + DR_PART * r;
+        S[r] = (j < dv && i < dk) ? srow[i] : 0.f;
+    }
+    const int col0 = tile * DR_COLS;
+
+    auto stage = [&](int c0, float* buf) {
+        const int nt = min(DL_CHUNK, len - c0);
+        float* qs = buf;
+        float* ks = qs + DL_CHUNK * dk;
+        float* gs = ks + DL_CHUNK * dk;
+        float* vs = gs + DL_CHUNK * dk;
+        float* bs = vs + DL_CHUNK * DR_COLS;
+        float* ds = bs + DL_CHUNK;
+        if (wide) {
+            const int dk4 = dk >> 2;
+            for (int idx = tid; idx < nt * dk4; idx += DR_COLS * DR_PART) {
+                const int t = idx / dk4, i = (idx - t * dk4) << 2;
+                const float* src = prep + (size_t)(row0 + c0 + t) * ldp;
+                dl_copy16(qs + t * dk + i, src + (size_t)hk * dk + i);
+                dl_copy16(ks + t * dk + i, src + qk + (size_t)hk * dk + i);
+                dl_copy16(gs + t * dk + i, src + 2 * qk + (size_t)h * dk + i);
+            }
+        } else {
+            for (int idx = tid; idx < nt * dk; idx += DR_COLS * DR_PART) {
+                const int t = idx / dk, i = idx - t * dk;
+                const float* src = prep + (size_t)(row0 + c0 + t) * ldp;
+                dl_copy4(qs + idx, src + (size_t)hk * dk + i);
+                dl_copy4(ks + idx, src + qk + (size_t)hk * dk + i);
+                dl_copy4(gs + idx, src + 2 * qk + (size_t)h * dk + i);
+            }
+        }
+        for (int idx = tid; idx < nt * DR_COLS; idx += DR_COLS * DR_PART) {
+            const int t = idx / DR_COLS, c = idx - t * DR_COLS;
+            if (col0 + c < dv) dl_copy4(vs + idx, v + (size_t)(row0 + c0 + t) * ldv + (size_t)h * dv + col0 + c);
+        }
+        if (tid < nt) {
+            const float* src = prep + (size_t)(row0 + c0 + tid) * ldp + 2 * qk + (size_t)n_heads * dk;
+            dl_copy4(bs + tid, src + h);
+            dl_copy4(ds + tid, src + n_heads + hk);
+        }
+    };
+
+    stage(0, dl_smem);
+    dl_commit();
+    int which = 0;
+    for (int c0 = 0; c0 < len; c0 += DL_CHUNK, which ^= 1) {
+        float* buf = dl_smem + which * per;
+        if (c0 + DL_CHUNK < len) {
+            stage(c0 + DL_CHUNK, dl_smem + (which ^ 1) * per);
+            dl_commit();
+            dl_wait<1>();
+        } else {
+            dl_wait<0>();
+        }
+        __syncthreads();
+        const int nt = min(DL_CHUNK, len - c0);
+        const float* qs = buf;
+        const float* ks = qs + DL_CHUNK * dk;
+        const float* gs = ks + DL_CHUNK * dk;
+        const float* vs = gs + DL_CHUNK * dk;
+        const float* bs = vs + DL_CHUNK * DR_COLS;
+        const float* ds = bs + DL_CHUNK;
+        for (int t = 0; t < nt; ++t) {
+            const float* qt = qs + t * dk;
+            const float* kt = ks + t * dk;
+            const float* gt = gs + t * dk;
+            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+            for (int r = 0; r < R; r += 2) {
+                const int i0 = p + DR_PART * r, i1 = i0 + DR_PART;
+                if (i0 < dk) {
+                    S[r] *= gt[i0];
+                    a0 = fmaf(S[r], kt[i0], a0);
+                    b0 = fmaf(S[r], qt[i0], b0);
+                }
+                if (r + 1 < R && i1 < dk) {
+                    S[r + 1] *= gt[i1];
+                    a1 = fmaf(S[r + 1], kt[i1], a1);
+                    b1 = fmaf(S[r + 1], qt[i1], b1);
+                }
+            }
+            float said = a0 + a1, read = b0 + b1;
+            said += __shfl_xor_sync(0xffffffffu, said, 1);
+            read += __shfl_xor_sync(0xffffffffu, read, 1);
+            said += __shfl_xor_sync(0xffffffffu, said, 2);
+            read += __shfl_xor_sync(0xffffffffu, read, 2);
+            said += __shfl_xor_sync(0xffffffffu, said, 4);
+            read += __shfl_xor_sync(0xffffffffu, read, 4);
+            const float u = bs[t] * ((j < dv ? vs[t * DR_COLS + jl] : 0.f) - said);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int i = p + DR_PART * r;
+                if (i < dk) S[r] = fmaf(kt[i], u, S[r]);
+            }
+            if (p == 0 && j < dv) o[(size_t)(row0 + c0 + t) * n_heads * dv + (size_t)h * dv + j] = fmaf(u, ds[t], read);
+        }
+        __syncthreads();
+    }
+    if (j < dv && mv_slot_ok(slots[sq])) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int i = p + DR_PART * r;
+            if (i < dk) srow[i] = S[r];
+        }
+    }
+}
+
+// Row width of `prep` for these sizes (a multiple of 4 floats, so that rows start on 16 bytes).
+static inline int mv_delta_prep_width(int n_heads, int kv_heads, int dk) {
+    const int w = 2 * kv_heads * dk + n_heads * dk + n_heads + kv_heads;
+    return (w + 3) & ~3;
+}
+
+// As mv_delta_scan, for steps of many tokens a sequence; prep [N, mv_delta_prep_width()] is scratch.
+MV_API int mv_delta_scan_long(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* b,
+                              int ldb, const float* a, int lda, const float* dt_bias, const float* a_log, float q_scale,
+                              float norm_eps, float* prep, float* state, const int* slots, const int* cu, float* o, int N,
+                              int n_seqs, int n_heads, int kv_heads, int dk, int dv, cudaStream_t stream) {
+    if (n_seqs <= 0 || N <= 0) return 0;
+    if (dk < 1 || dk > 256 || dv < 1 || kv_heads < 1 || n_heads % kv_heads) return (int)cudaErrorInvalidValue;
+    const int ldp = mv_delta_prep_width(n_heads, kv_heads, dk);
+    mv_launch(delta_prepare_kernel, N, 256, 0, stream, q, ldq, k, ldk, b, ldb, a, lda, dt_bias, a_log, q_scale, norm_eps, prep,
+              ldp, n_heads, kv_heads, dk);
+    const dim3 grid((dv + DR_COLS - 1) / DR_COLS, n_heads, n_seqs);
+    const size_t smem = 2 * (size_t)DL_CHUNK * (3 * dk + DR_COLS + 2) * sizeof(float);
+    // 16-byte copies: every row of q, k and g of a head starts on 16 bytes (ldp is a multiple of 4 floats)
+    const int wide = dk % 4 == 0 && (((uintptr_t)prep) & 15) == 0;
+#define DL_LAUNCH(R)                                                                                                     \
+    do {                                                                                                                 \
+        if (smem > 48 * 1024) {                                                                                          \
+            const cudaError_t e = cudaFuncSetAttribute(delta_scan_long_kernel<R>,                                        \
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
+            if (e != cudaSuccess) return (int)e;                                                                         \
+        }                                                                                                                \
+        mv_launch(delta_scan_long_kernel<R>, grid, DR_COLS * DR_PART, smem, stream, (const float*)prep, ldp, v, ldv, state, \
+                  slots, cu, o, n_heads, kv_heads, dk, dv, wide);                                                        \
+    } while (0)
+    if (dk <= 32) DL_LAUNCH(4);
+    else if (dk <= 64) DL_LAUNCH(8);
+    else if (dk <= 128) DL_LAUNCH(16);
+    else DL_LAUNCH(32);
+#undef DL_LAUNCH
+    return mv_launch_status();
+}

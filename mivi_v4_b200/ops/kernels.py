@@ -82,6 +82,7 @@ _SIGNATURES = {
         "mv_latent_prepare": [_P, _I, _I, _I, _P, _F, _P, _P, _P, _P, _I, _I, _P, _Q, _I, _P, _I, _I, _I, _I, _I, _I, _P],
         "mv_head_product": [_P, _Q, _I, _P, _I, _I, _P, _Q, _P, _I, _Q, _I, _I, _I, _I, _I, _P],
         "mv_latent_attention": [_P, _P, _Q, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+        "mv_delta_scan_long": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _F, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
         "mv_delta_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _F, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "mv_expert_rank": [_P, _I, _I, _P, _P, _P],
         "mv_expert_gather": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
@@ -1140,25 +1141,45 @@ def latent_attention(qa: torch.Tensor, pool: torch.Tensor, page_size: int, page_
     return out
 
 
+# steps that bring a sequence this many tokens or more run the recurrence from rows prepared by a kernel before it
+DELTA_LONG_STEP = 8
+
+
 def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, a: torch.Tensor,
                dt_bias: torch.Tensor, a_log: torch.Tensor, state: torch.Tensor, slots, cu, out: torch.Tensor,
                n_seqs: int, n_heads: int, kv_heads: int, dk: int, dv: int, *, q_scale: float,
-               norm_eps: float = 1e-6) -> torch.Tensor:
+               norm_eps: float = 1e-6, max_len: int = 1, ws=None) -> torch.Tensor:
     """The gated delta rule with a decay per key channel, token by token: per head S <- diag(g) S;
     u = sigmoid(beta) (v - S^T k); S <- S + k u^T; o = S^T q, with q and k made unit vectors per head first
     (x / sqrt(sum x^2 + norm_eps), q also times ``q_scale``) and g = exp(-exp(a_log_h) softplus(a + dt_bias)).
     q, k [N, kv_heads * dk] (head h reads head h // (n_heads / kv_heads)), v [N, n_heads * dv], beta [N, n_heads],
     a [N, n_heads * dk]: float32, column slices are fine; ``state`` float32 [slots, n_heads, dv, dk]; ``out``
-    float32 [N, n_heads * dv]."""
+    float32 [N, n_heads * dv].  ``max_len``: the most tokens that a sequence brings; from ``DELTA_LONG_STEP`` on
+    (and with a workspace ``ws`` for the prepared rows) unit vectors, decays and beta are worked out once a token by
+    a kernel of their own and the walk along the sequence holds the recurrence alone."""
     N = out.shape[0]
     if not 1 <= dk <= MAX_SCAN_KEY_DIM or kv_heads < 1 or n_heads % kv_heads:
         raise KernelError(f"delta_scan: key size {dk} (1..{MAX_SCAN_KEY_DIM}), {n_heads} heads on {kv_heads} kv heads")
+    long_step = ws is not None and max_len >= DELTA_LONG_STEP
     qp, ldq = _cols(q, "delta_scan q", N, kv_heads * dk)
     kp, ldk = _cols(k, "delta_scan k", N, kv_heads * dk)
     vp, ldv = _cols(v, "delta_scan v", N, n_heads * dv)
     bp, ldb = _cols(beta, "delta_scan beta", N, n_heads)
     ap, lda = _cols(a, "delta_scan decay", N, n_heads * dk)
     _guard("core", "delta_rule", out.device, n_slots=state.shape[0])
+    if long_step:
+        # a row: q and k of the q/k heads, the decays, beta, k . q; padded to 16 bytes (as the kernel lays it out)
+        width = (2 * kv_heads * dk + n_heads * dk + n_heads + kv_heads + 3) & ~3
+        prep = ws.get("delta_scan.prep", (N, width), torch.float32)
+        _check(_fn("core", "mv_delta_scan_long")(
+            qp, ldq, kp, ldk, vp, ldv, bp, ldb, ap, lda, _need(dt_bias, "dt_bias", torch.float32, (n_heads * dk,)),
+            _need(a_log, "A_log", torch.float32, (n_heads,)), float(q_scale), float(norm_eps), prep.data_ptr(),
+            _need(state, "delta_scan state", torch.float32, (None, n_heads, dv, dk)), _need(slots, "slots", torch.int32),
+            _need(cu, "cu", torch.int32), _need(out, "delta_scan out", torch.float32, (N, n_heads * dv)), N, int(n_seqs),
+            n_heads, kv_heads, dk, dv, _stream()), "mv_delta_scan_long")
+        account(2 * n_seqs * n_heads * dv * dk * 4 + N * (2 * kv_heads * dk + n_heads * (2 * dv + dk + 1)) * 4
+                + 2 * prep.numel() * 4, 6 * N * n_heads * dk * dv)
+        return out
     _check(_fn("core", "mv_delta_scan")(
         qp, ldq, kp, ldk, vp, ldv, bp, ldb, ap, lda, _need(dt_bias, "dt_bias", torch.float32, (n_heads * dk,)),
         _need(a_log, "A_log", torch.float32, (n_heads,)), float(q_scale), float(norm_eps),

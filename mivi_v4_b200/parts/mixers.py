@@ -758,7 +758,7 @@ class ChannelDelta(Part):
         o = self.scratch(step, "o", (N, vv), torch.float32)
         K.delta_scan(xbc[:, :qk], xbc[:, qk:2 * qk], xbc[:, 2 * qk:], proj[:, C:C + nh], up[:, :hk], self.dt_bias,
                      self.a_log, memory.state, step.slots, step.cu, o, step.n_seqs, nh, nkv, dk, dv,
-                     q_scale=dk ** -0.5, norm_eps=self.UNIT_EPS)
+                     q_scale=dk ** -0.5, norm_eps=self.UNIT_EPS, max_len=step.max_len, ws=step.ws)
         y = self.scratch(step, "mix", (N, vv), step.dtype)
         K.gated_rmsnorm(o, up[:, hk:hk + vv], self.norm, dv, self.eps, K.GATE_SIGMOID, y)
         linear(y, self.w_o, resid, accumulate=accumulate)
