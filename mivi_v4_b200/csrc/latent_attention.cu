@@ -61,6 +61,7 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, int q0, int c0, co
         }
         for (int i = rot_dims + threadIdx.x; i < rot; i += blockDim.x) dst[rank + i] = mv_from_f32<T>(r[i]);
     }
+    if (!qa) return;                       // the queries are prepared elsewhere
     for (int e = threadIdx.x; e < nh * half; e += blockDim.x) {
         const int h = e / half, i = e - h * half;
         const float* qr = row + q0 + (size_t)h * (dim + rot) + dim;
@@ -197,7 +198,7 @@ latent_attention_kernel(const float* __restrict__ qa, const T* __restrict__ pool
                         const int* __restrict__ page_table, int table_stride, int page_shift,
                         const int* __restrict__ positions, const int* __restrict__ seq_of,
                         const float* __restrict__ sinks, float* __restrict__ out, int nh, int rank, int rot, float scale,
-                        int window) {
+                        int window, int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
     mv_pdl_begin();
     extern __shared__ float la_smem[];
     const int w = rank + rot;
@@ -211,17 +212,25 @@ latent_attention_kernel(const float* __restrict__ qa, const T* __restrict__ pool
     const int* table = page_table + (size_t)seq_of[n] * table_stride;
     const int page_mask = (1 << page_shift) - 1;
     for (int e = threadIdx.x; e < heads * w; e += blockDim.x) qs[e] = qa[((size_t)n * nh + h0) * w + e];
-    const int j_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    int j_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    int j_hi = pos;
+    const int split = blockIdx.z;
+    if (splits > 1) {                                           // this block's share of the keys, whole tiles of LA_KEYS
+        const int per = ((pos - j_lo + splits) / splits + LA_KEYS - 1) / LA_KEYS * LA_KEYS;
+        j_lo += split * per;
+        j_hi = min(pos, j_lo + per - 1);
+    }
     const bool active = warp < heads;
     const int h = h0 + warp;
-    float m = (active && sinks) ? sinks[h] : -INFINITY;
-    float l = (active && sinks) ? 1.f : 0.f;
+    const bool with_sink = active && sinks && split == 0;       // the sink counts once: in the first share
+    float m = with_sink ? sinks[h] : -INFINITY;
+    float l = with_sink ? 1.f : 0.f;
     float acc[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) acc[r] = 0.f;
     const float* q = qs + warp * w;
-    for (int j0 = j_lo; j0 <= pos; j0 += LA_KEYS) {
-        const int nk = min(LA_KEYS, pos - j0 + 1);
+    for (int j0 = j_lo; j0 <= j_hi; j0 += LA_KEYS) {
+        const int nk = min(LA_KEYS, j_hi - j0 + 1);
         __syncthreads();
         for (int e = threadIdx.x; e < nk * w; e += blockDim.x) {
             const int r = e / w, c = e - r * w;
@@ -255,7 +264,19 @@ latent_attention_kernel(const float* __restrict__ qa, const T* __restrict__ pool
             }
         }
     }
-    if (active) {
+    if (active && splits > 1) {                                 // unnormalised sums, maximum and denominator of the share
+        const size_t at = ((size_t)n * nh + h) * splits + split;
+        float* o = part_o + at * rank;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int c = lane + 32 * r;
+            if (c < rank) o[c] = acc[r];
+        }
+        if (lane == 0) {
+            part_ml[2 * at] = m;
+            part_ml[2 * at + 1] = l;
+        }
+    } else if (active) {
         const float inv = l > 0.f ? 1.0f / l : 0.f;
         float* o = out + ((size_t)n * nh + h) * rank;
 #pragma unroll
@@ -266,19 +287,46 @@ latent_attention_kernel(const float* __restrict__ qa, const T* __restrict__ pool
     }
 }
 
+// The shares of one (token, head) put together: out = sum_z acc_z exp(m_z - M) / sum_z l_z exp(m_z - M), M = max m_z.
+__global__ void __launch_bounds__(128)
+latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, float* __restrict__ out,
+                              int rank, int splits) {
+    mv_pdl_begin();
+    const size_t at = (size_t)blockIdx.x * splits;
+    float M = -INFINITY;
+    for (int z = 0; z < splits; ++z) M = fmaxf(M, part_ml[2 * (at + z)]);
+    float L = 0.f;
+    for (int z = 0; z < splits; ++z) {
+        const float mz = part_ml[2 * (at + z)];
+        if (mz != -INFINITY) L += part_ml[2 * (at + z) + 1] * expf(mz - M);
+    }
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        float a = 0.f;
+        for (int z = 0; z < splits; ++z) {
+            const float mz = part_ml[2 * (at + z)];
+            if (mz != -INFINITY) a = fmaf(part_o[(at + z) * rank + c], expf(mz - M), a);
+        }
+        out[(size_t)blockIdx.x * rank + c] = a * inv;
+    }
+}
+
 // qa [N, nh, rank + rot] and out [N, nh, rank], 32-bit; pool: pages of [row][rank + rot] in `dtype`; sinks [nh] or null.
+// splits > 1: every (token, head tile) is `splits` blocks, each over its share of the keys, and a second kernel puts
+// the shares together; part_o [N, nh, splits, rank] and part_ml [N, nh, splits, 2] are their scratch.
 MV_API int mv_latent_attention(const float* qa, const void* pool, long long page_stride, int dtype, const int* page_table,
                                int table_stride, int page_size, const int* positions, const int* seq_of,
                                const float* sinks, float* out, int N, int nh, int rank, int rot, float scale, int window,
-                               cudaStream_t stream) {
+                               int splits, float* part_o, float* part_ml, cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (rank < 1 || rank > 32 * LA_MAX_OUT || rot < 0 || page_size < 1 || (page_size & (page_size - 1)) || window < 0)
+    if (rank < 1 || rank > 32 * LA_MAX_OUT || rot < 0 || page_size < 1 || (page_size & (page_size - 1)) || window < 0 ||
+        splits < 1 || splits > 65535 || (splits > 1 && (!part_o || !part_ml)))
         return (int)cudaErrorInvalidValue;
     int shift = 0;
     while ((1 << shift) < page_size) ++shift;
     const int w = rank + rot;
     const size_t smem = sizeof(float) * ((size_t)LA_HEADS * w + (size_t)LA_KEYS * (w | 1));
-    const dim3 grid(N, (nh + LA_HEADS - 1) / LA_HEADS);
+    const dim3 grid(N, (nh + LA_HEADS - 1) / LA_HEADS, splits);
 #define LA_LAUNCH(T, R)                                                                                                   \
     do {                                                                                                                  \
         if (smem > 48 * 1024) {                                                                                           \
@@ -287,7 +335,8 @@ MV_API int mv_latent_attention(const float* qa, const void* pool, long long page
             if (e != cudaSuccess) return (int)e;                                                                          \
         }                                                                                                                 \
         mv_launch(latent_attention_kernel<T, R>, grid, LA_HEADS * 32, smem, stream, qa, (const T*)pool, page_stride,      \
-                  page_table, table_stride, shift, positions, seq_of, sinks, out, nh, rank, rot, scale, window);          \
+                  page_table, table_stride, shift, positions, seq_of, sinks, out, nh, rank, rot, scale, window, splits,  \
+                  part_o, part_ml);                                                                                       \
     } while (0)
 #define LA_BY_RANK(T)                                                                                                     \
     do {                                                                                                                  \
@@ -299,5 +348,11 @@ MV_API int mv_latent_attention(const float* qa, const void* pool, long long page
     if (dtype == MV_DT_BF16) LA_BY_RANK(__nv_bfloat16); else LA_BY_RANK(float);
 #undef LA_BY_RANK
 #undef LA_LAUNCH
+    if (splits > 1) {
+        const int e = mv_launch_status();
+        if (e) return e;
+        mv_launch(latent_attention_merge_kernel, N * nh, 128, 0, stream, (const float*)part_o, (const float*)part_ml, out,
+                  rank, splits);
+    }
     return mv_launch_status();
 }

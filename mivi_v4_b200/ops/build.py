@@ -30,7 +30,8 @@ LIBRARIES: Dict[str, List[str]] = {
              "sampling.cu", "gated_norms.cu", "decay_scan.cu", "attention_sink.cu", "scalar_scan.cu", "state_space.cu",
              "routed_experts.cu", "latent_attention.cu", "delta_rule.cu"],
     "bf16": ["gemm_small_m.cu", "gemm_tc.cu", "gemm_tc_pair.cu", "gemm_tc_swap.cu", "attention_prefill.cu",
-             "attention_prefill_tc.cu", "attention_decode_tc.cu", "attention_sink_prefill.cu"],
+             "attention_prefill_tc.cu", "attention_decode_tc.cu", "attention_sink_prefill.cu",
+             "latent_attention_prefill.cu"],
 }
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -11,7 +11,7 @@ from __future__ import annotations
 import ctypes
 import os
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -81,7 +81,7 @@ _SIGNATURES = {
         "mv_add_rows_vector": [_P, _P, _P, _I, _I, _P],
         "mv_latent_prepare": [_P, _I, _I, _I, _P, _F, _P, _P, _P, _P, _I, _I, _P, _Q, _I, _P, _I, _I, _I, _I, _I, _I, _P],
         "mv_head_product": [_P, _Q, _I, _P, _I, _I, _P, _Q, _P, _I, _Q, _I, _I, _I, _I, _I, _P],
-        "mv_latent_attention": [_P, _P, _Q, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+        "mv_latent_attention": [_P, _P, _Q, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
         "mv_delta_scan_long": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _F, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
         "mv_delta_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _F, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "mv_expert_rank": [_P, _I, _I, _P, _P, _P],
@@ -109,6 +109,9 @@ _SIGNATURES = {
                                       _I, _I, _P],
         "mv_attention_decode_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
         "mv_attention_prefill_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P, _P],
+        "mv_latent_query": [_P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "mv_latent_gather": [_P, _Q, _P, _I, _I, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P],
+        "mv_latent_attention_prefill": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     },
 }
 _fns = {}
@@ -1077,9 +1080,9 @@ def latent_prepare(proj: torch.Tensor, q0: int, c0: int, w_c: torch.Tensor, eps:
     every head's last ``rot`` of q rotated (their first ``rot_dims``, all by default: element i with i + rot_dims / 2,
     angle pos * inv_freq[i]; the others pass unchanged); the row [rank + rot]
     goes into the token's place of its page, the rotated parts of q into the last ``rot`` columns of ``qa``
-    [N, nh, rank + rot] (float32)."""
-    N = qa.shape[0]
-    if (not proj.is_cuda or proj.dtype != torch.float32 or proj.dim() != 2 or proj.shape[0] != N or proj.stride(1) != 1
+    [N, nh, rank + rot] (float32; None: the queries are prepared elsewhere)."""
+    N = proj.shape[0]
+    if (not proj.is_cuda or proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1
             or q0 < 0 or q0 + nh * (dim + rot) > proj.shape[1] or c0 < 0 or c0 + rank + rot > proj.shape[1]):
         raise KernelError(f"latent_prepare: projection {proj.dtype} {tuple(proj.shape)} does not hold q at {q0} and the "
                           f"latent at {c0} for {N} rows")
@@ -1094,7 +1097,7 @@ def latent_prepare(proj: torch.Tensor, q0: int, c0: int, w_c: torch.Tensor, eps:
         float(eps), _need(inv_freq, "inv_freq", torch.float32, (rot_dims // 2,), rot_dims == 0),
         _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
         _need(page_table, "page table", torch.int32), page_table.shape[1], int(page_size), pool.data_ptr(), pool.stride(0),
-        _dt(pool), _need(qa, "absorbed q", torch.float32, (N, nh, rank + rot)), N, nh, dim, rot, rank, rot_dims, _stream()),
+        _dt(pool), _need(qa, "absorbed q", torch.float32, (N, nh, rank + rot), True), N, nh, dim, rot, rank, rot_dims, _stream()),
         "mv_latent_prepare")
     account(N * (nh * rot * 8 + (rank + rot) * (4 + pool.element_size())))
 
@@ -1120,24 +1123,109 @@ def head_product(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, nh: int, n_i
     return y
 
 
+# a (token, head tile) whose keys would keep one block busy for more than this many of them is cut into shares
+LATENT_SPLIT_KEYS = 256
+LATENT_MAX_SPLITS = 32
+
+
+def latent_splits(n_tokens: int, n_heads: int, longest: int, sm_count: int) -> int:
+    """Into how many shares of the keys a step of ``n_tokens`` query tokens is cut: enough blocks to fill the device
+    twice, no share under ``LATENT_SPLIT_KEYS`` keys."""
+    blocks = max(1, n_tokens * ((n_heads + 7) // 8))
+    want = (2 * sm_count + blocks - 1) // blocks
+    return int(max(1, min(want, longest // LATENT_SPLIT_KEYS, LATENT_MAX_SPLITS)))
+
+
 def latent_attention(qa: torch.Tensor, pool: torch.Tensor, page_size: int, page_table, positions, seq_of,
                      out: torch.Tensor, nh: int, rank: int, rot: int, scale: float, *, window: int = 0,
-                     sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     sinks: Optional[torch.Tensor] = None, splits: int = 1,
+                     part: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
     """Causal softmax attention of every token of the step over its sequence's cached rows [rank + rot] (which already
     hold the step's own): all heads read the same rows as keys, and the rows' first ``rank`` numbers as values.
     ``qa`` float32 [N, nh, rank + rot], ``out`` float32 [N, nh, rank].  ``window`` w > 0: query i reads key j if
-    0 <= i - j < w.  ``sinks`` [nh]: exp(sink) joins each head's denominator.  Scores and softmax are float32."""
+    0 <= i - j < w.  ``sinks`` [nh]: exp(sink) joins each head's denominator.  Scores and softmax are float32.
+    ``splits`` > 1: the keys of every token are cut into that many shares, one block each, and a second kernel puts
+    the shares together; ``part`` = (float32 [N, nh, splits, rank], float32 [N, nh, splits, 2]) is their scratch."""
     N = qa.shape[0]
     if not 1 <= rank <= LATENT_MAX_RANK or rot < 0:
         raise KernelError(f"latent_attention: rank {rank} must lie in 1..{LATENT_MAX_RANK}")
     _check_latent_pool(pool, page_size, rank + rot, "latent_attention")
+    splits = int(splits)
+    if splits > 1 and part is None:
+        raise KernelError("latent_attention: shares of the keys need their scratch")
     _guard("core", "latent_attention", qa.device, n_pages=pool.shape[0])
     _check(_fn("core", "mv_latent_attention")(
         _need(qa, "absorbed q", torch.float32, (N, nh, rank + rot)), pool.data_ptr(), pool.stride(0), _dt(pool),
         _need(page_table, "page table", torch.int32), page_table.shape[1], int(page_size),
         _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
         _need(sinks, "sinks", torch.float32, (nh,), True), _need(out, "attention out", torch.float32, (N, nh, rank)),
-        N, nh, rank, rot, float(scale), int(window), _stream()), "mv_latent_attention")
+        N, nh, rank, rot, float(scale), int(window), splits,
+        _need(part[0], "shares", torch.float32, (N, nh, splits, rank)) if splits > 1 else None,
+        _need(part[1], "shares' sums", torch.float32, (N, nh, splits, 2)) if splits > 1 else None,
+        _stream()), "mv_latent_attention")
+    return out
+
+
+def latent_prefill_fits(dim: int, rot: int, dv: int, rank: int) -> bool:
+    """Whether the tensor-core kernels for steps of many tokens take these sizes."""
+    return dim % 8 == 0 and rot % 8 == 0 and (dim + rot) % 16 == 0 and 16 <= dim + rot <= 192 and dv % 16 == 0 \
+        and 16 <= dv <= 128 and rank % 8 == 0
+
+
+def latent_query(proj: torch.Tensor, q0: int, inv_freq: Optional[torch.Tensor], positions, q: torch.Tensor, nh: int,
+                 dim: int, rot: int, rot_dims: int) -> torch.Tensor:
+    """``q`` [N, nh, dim + rot] (bfloat16) from float32 rows of a projection (the queries from column ``q0``), the first
+    ``rot_dims`` of every head's last ``rot`` elements turned (i with i + rot_dims / 2, angle pos * inv_freq[i])."""
+    N = q.shape[0]
+    if (not proj.is_cuda or proj.dtype != torch.float32 or proj.dim() != 2 or proj.shape[0] != N or proj.stride(1) != 1
+            or q0 < 0 or q0 + nh * (dim + rot) > proj.shape[1] or rot_dims % 2 or not 0 <= rot_dims <= rot):
+        raise KernelError(f"latent_query: projection {proj.dtype} {tuple(proj.shape)} does not hold {nh} heads of "
+                          f"{dim} + {rot} at {q0} for {N} rows")
+    _check(_fn("bf16", "mv_latent_query")(
+        proj.data_ptr(), proj.stride(0), int(q0), _need(inv_freq, "inv_freq", torch.float32, (rot_dims // 2,), rot_dims == 0),
+        _need(positions, "positions", torch.int32), _need(q, "q", torch.bfloat16, (N, nh, dim + rot)), N, nh, dim, rot,
+        int(rot_dims), _stream()), "mv_latent_query")
+    account(N * nh * (dim + rot) * 6)
+    return q
+
+
+def latent_gather(pool: torch.Tensor, page_size: int, page_table, cu, starts, n_seqs: int, window: int,
+                  c: torch.Tensor, r: torch.Tensor) -> None:
+    """The cached rows [rank | rot] that the step's tokens can see (sequence b's positions from
+    max(0, starts[b] - window + 1), from 0 without a window, to its last), sequence after sequence, into ``c``
+    [rows, rank] and ``r`` [rows, rot], bfloat16."""
+    rows, rank, rot = c.shape[0], c.shape[1], r.shape[1]
+    _check_latent_pool(pool, page_size, rank + rot, "latent_gather")
+    if pool.dtype != torch.bfloat16:
+        raise KernelError(f"latent_gather: the cache is {pool.dtype}, expected bfloat16")
+    _guard("bf16", "latent_attention_prefill", pool.device, n_pages=pool.shape[0])
+    _check(_fn("bf16", "mv_latent_gather")(
+        pool.data_ptr(), pool.stride(0), _need(page_table, "page table", torch.int32), page_table.shape[1], int(page_size),
+        _need(cu, "cu", torch.int32), _need(starts, "starts", torch.int32), int(n_seqs), int(window), rank, rot,
+        _need(c, "latents", torch.bfloat16, (rows, rank)), _need(r, "rotated keys", torch.bfloat16, (rows, rot)), rows,
+        _stream()), "mv_latent_gather")
+    account(rows * (rank + rot) * 4)
+
+
+def latent_attention_prefill(q: torch.Tensor, kx: torch.Tensor, v0: int, r: torch.Tensor, cu, starts, n_seqs: int,
+                             out: torch.Tensor, nh: int, dim: int, rot: int, dv: int, scale: float, *, window: int = 0,
+                             sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal softmax attention on the tensor cores for steps of many tokens: ``q`` [N, nh, dim + rot] against the
+    gathered rows' keys and values ``kx`` [rows, >= v0 + nh dv] (head h's unrotated key at column h dim, its value at
+    v0 + h dv) and the shared rotated key part ``r`` [rows, rot]; all bfloat16, scores and softmax float32.
+    ``gate``: float32 logits [N, nh dv] (a column slice is fine); ``out`` [N, nh dv] is multiplied by their sigmoid."""
+    N, rows = q.shape[0], kx.shape[0]
+    if not latent_prefill_fits(dim, rot, dv, 8):
+        raise KernelError(f"latent_attention_prefill: sizes {dim} + {rot}, {dv} are not served")
+    if kx.dtype != torch.bfloat16 or kx.dim() != 2 or kx.stride(1) != 1 or kx.shape[1] < v0 + nh * dv or v0 < nh * dim:
+        raise KernelError(f"latent_attention_prefill: keys and values {kx.dtype} {tuple(kx.shape)}, values from {v0}")
+    gp, ldg = _cols(gate, "latent_attention_prefill gate", N, nh * dv) if gate is not None else (None, 0)
+    _check(_fn("bf16", "mv_latent_attention_prefill")(
+        _need(q, "q", torch.bfloat16, (N, nh, dim + rot)), kx.data_ptr(), kx.stride(0), int(v0),
+        _need(r, "rotated keys", torch.bfloat16, (rows, rot)), _need(cu, "cu", torch.int32),
+        _need(starts, "starts", torch.int32), _need(sinks, "sinks", torch.float32, (nh,), True), gp, ldg,
+        _need(out, "attention out", torch.bfloat16, (N, nh * dv)), N, int(n_seqs), nh, dim, rot, dv, float(scale),
+        int(window), _stream()), "mv_latent_attention_prefill")
     return out
 
 

@@ -639,9 +639,21 @@ class LatentAttention(Part):
         self.w_in = _fuse_rows([t["q"], t["dkv"]] + ([t["g"]] if self.gated else []))
         self.c_norm, self.sinks, self.w_o = t["dkv.norm"], t.get("sink"), t["o"]
         self.w_uk, self.w_uv = t["uk"].contiguous(), t["uv"].contiguous()
+        # steps of many tokens build every head's keys and values from the cached rows with one product
+        self.w_kv = None
+        if self.w_uk.dtype == torch.bfloat16 and K.latent_prefill_fits(self.dim, self.rd, self.dv, self.rank):
+            self.w_kv = _fuse_rows([self.w_uk, self.w_uv])
 
     def cache_need(self):
         return KVNeed(1, self.rank + self.rd, self.window, self.rank, values_in_keys=True)
+
+    # a step takes the tensor-core path when a sequence brings this many tokens and the cached rows it has to turn
+    # into keys and values are at most this many times its tokens
+    LONG_STEP, LONG_ROWS = 16, 4
+
+    def _seen_rows(self, step) -> int:
+        w = self.window
+        return sum(s + n - (max(0, s - w + 1) if w else 0) for s, n in zip(step.host_starts, step.host_lens))
 
     def forward(self, u, resid, step, view, accumulate: bool = True) -> None:
         N = u.shape[0]
@@ -651,22 +663,51 @@ class LatentAttention(Part):
         proj = self.scratch(step, "proj", (N, self.w_in.shape[0]), torch.float32)
         linear(u, self.w_in, proj)
         rot = self.position.rotary(u.device) if self.rot_dims else None
-        qa = self.scratch(step, "qa", (N, nh, rank + rd), torch.float32)
-        K.latent_prepare(proj, 0, c0, self.c_norm, self.eps, rot[0] if rot is not None else None, step.positions,
-                         step.seq_of, view.page_table, view.pool, view.page_size, qa, nh, dim, rd, rank, self.rot_dims)
-        K.head_product(proj[:, :c0].unflatten(1, (nh, dim + rd)), self.w_uk, qa, nh, dim, rank, transposed=True)
-        o_lat = self.scratch(step, "o_lat", (N, nh, rank), torch.float32)
-        K.latent_attention(qa, view.pool, view.page_size, view.page_table, step.positions, step.seq_of, o_lat, nh, rank,
-                           rd, self.scale, window=self.window, sinks=self.sinks)
+        inv_freq = rot[0] if rot is not None else None
+        gate = proj[:, g0:g0 + nh * dv] if self.gated else None
+        y = self.scratch(step, "mix", (N, nh * dv), step.dtype)
+        rows = self._seen_rows(step) if step.max_len >= self.LONG_STEP else 0
         if K.profiling_on():
             reach = self.window or None
             pairs = sum(sum(min(s + i + 1, reach) if reach else s + i + 1 for i in range(n))
                         for s, n in zip(step.host_starts, step.host_lens))
+        if (self.w_kv is not None and step.dtype == torch.bfloat16 and view.pool.dtype == torch.bfloat16
+                and 0 < rows <= self.LONG_ROWS * N):
+            K.latent_prepare(proj, 0, c0, self.c_norm, self.eps, inv_freq, step.positions, step.seq_of, view.page_table,
+                             view.pool, view.page_size, None, nh, dim, rd, rank, self.rot_dims)
+            q = self.scratch(step, "q", (N, nh, dim + rd), torch.bfloat16)
+            K.latent_query(proj, 0, inv_freq, step.positions, q, nh, dim, rd, self.rot_dims)
+            c = self.scratch(step, "c", (rows, rank), torch.bfloat16)
+            r = self.scratch(step, "r", (rows, rd), torch.bfloat16)
+            K.latent_gather(view.pool, view.page_size, view.page_table, step.cu, step.starts, step.n_seqs, self.window, c, r)
+            kx = self.scratch(step, "kx", (rows, self.w_kv.shape[0]), torch.bfloat16)
+            linear(c, self.w_kv, kx)
+            K.latent_attention_prefill(q, kx, nh * dim, r, step.cu, step.starts, step.n_seqs, y, nh, dim, rd, dv,
+                                       self.scale, window=self.window, sinks=self.sinks, gate=gate)
+            if K.profiling_on():
+                K.account(N * nh * (dim + rd + dv) * 2 + rows * nh * (dim + dv) * 2 + rows * rd * 2,
+                          2 * nh * (dim + rd + 2 * dv) * pairs)
+            linear(y, self.w_o, resid, accumulate=accumulate)
+            return
+        qa = self.scratch(step, "qa", (N, nh, rank + rd), torch.float32)
+        K.latent_prepare(proj, 0, c0, self.c_norm, self.eps, inv_freq, step.positions, step.seq_of, view.page_table,
+                         view.pool, view.page_size, qa, nh, dim, rd, rank, self.rot_dims)
+        K.head_product(proj[:, :c0].unflatten(1, (nh, dim + rd)), self.w_uk, qa, nh, dim, rank, transposed=True)
+        o_lat = self.scratch(step, "o_lat", (N, nh, rank), torch.float32)
+        # few query tokens with many keys each: the keys in shares.  The number of shares follows from what the page
+        # table can hold, not from the lengths of the moment, so that a recorded step stays right as they grow.
+        longest = view.page_table.shape[1] * view.page_size
+        splits = K.latent_splits(N, nh, min(longest, self.window) if self.window else longest, K.n_sms())
+        part = None
+        if splits > 1:
+            part = (self.scratch(step, "part_o", (N, nh, splits, rank), torch.float32),
+                    self.scratch(step, "part_ml", (N, nh, splits, 2), torch.float32))
+        K.latent_attention(qa, view.pool, view.page_size, view.page_table, step.positions, step.seq_of, o_lat, nh, rank,
+                           rd, self.scale, window=self.window, sinks=self.sinks, splits=splits, part=part)
+        if K.profiling_on():
             K.account((rank + rd) * view.pool.element_size() * pairs + N * nh * (2 * rank + rd) * 4,
                       2 * nh * (2 * rank + rd) * pairs)
-        y = self.scratch(step, "mix", (N, nh * dv), step.dtype)
-        K.head_product(o_lat, self.w_uv, y.view(N, nh, dv), nh, rank, dv,
-                       gate=proj[:, g0:g0 + nh * dv] if self.gated else None)
+        K.head_product(o_lat, self.w_uv, y.view(N, nh, dv), nh, rank, dv, gate=gate)
         linear(y, self.w_o, resid, accumulate=accumulate)
 
 

@@ -149,7 +149,7 @@ def _latent_case(T, H, dim, rd, vd, rank, window, rot_dims, base, scale, seed, l
     return h, p, m, P.latent_attention(h, p, m, 1e-5)
 
 
-def _run_latent(k, dtype, h, p, m, cuts, page_size, sink=True):
+def _run_latent(k, dtype, h, p, m, cuts, page_size, sink=True, splits=1):
     from mivi_v4_b200.parts.position import Rope
     T = h.shape[0]
     H, dim, rd, vd, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
@@ -170,8 +170,9 @@ def _run_latent(k, dtype, h, p, m, cuts, page_size, sink=True):
                          rank, rot["dims"])
         k.head_product(proj[rows][:, :c0].unflatten(1, (H, dim + rd)), dev(p["uk"], dtype), qa, H, dim, rank, transposed=True)
         o_lat = torch.full((n, H, rank), float("nan"), device=DEV)
+        part = (torch.full((n, H, splits, rank), float("nan"), device=DEV), torch.full((n, H, splits, 2), float("nan"), device=DEV))
         k.latent_attention(qa, pool, page_size, table, pos, seq_of, o_lat, H, rank, rd, m["scale"], window=window,
-                           sinks=dev(p["sink"]) if sink else None)
+                           sinks=dev(p["sink"]) if sink else None, splits=splits, part=part if splits > 1 else None)
         y = torch.full((n, H * vd), float("nan"), dtype=dtype, device=DEV)
         k.head_product(o_lat, dev(p["uv"], dtype), y.view(n, H, vd), H, rank, vd, gate=proj[rows][:, g0:g0 + H * vd])
         outs.append(y)
@@ -210,6 +211,113 @@ def test_a_loud_key_far_away_and_just_inside_and_just_outside_a_window(dtype):
         v_key = (c @ p["uv"].T)[0] * torch.sigmoid(h[139, H * (dim + rd) + rank + rd:])
         near = (want[139] - v_key).abs().max() < 0.05 * v_key.abs().max()
         assert bool(near) == seen, (window, key)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("splits", [2, 3, 7])
+def test_keys_in_shares_give_the_same_attention(dtype, splits):
+    """Shares that end inside a window, shares with no key at all (more shares than blocks of keys) and the sink
+    counted once."""
+    k = K()
+    tol = 3e-5 if dtype == torch.float32 else 2e-2
+    for T, window in ((170, 0), (170, 70), (40, 0), (3, 0)):
+        h, p, m, want = _latent_case(T, 3, 8, 8, 8, 24, window, 8, 1e4, 0.4, seed=T + window)
+        for cuts in ([T], [T - 2, 1, 1]):
+            close(_run_latent(k, dtype, h, p, m, cuts, 16, splits=splits), want, tol, f"{splits} shares, window {window}")
+        close(_run_latent(k, dtype, h, p, dict(m), [T], 16, sink=False, splits=splits),
+              P.latent_attention(h, dict(p, sink=torch.full((3,), -800.0, dtype=F64)), m, 1e-5), tol, "no sink")
+
+
+def test_number_of_shares_follows_the_work():
+    k = K()
+    assert k.latent_splits(2048, 32, 4096, 148) == 1                 # many tokens fill the device by themselves
+    assert k.latent_splits(8, 32, 100, 148) == 1                     # nothing to cut
+    assert 2 <= k.latent_splits(8, 32, 4096, 148) <= k.LATENT_MAX_SPLITS
+    assert k.latent_splits(1, 8, 1 << 20, 148) == k.LATENT_MAX_SPLITS
+
+
+def _run_latent_long(k, h_seqs, p, m, steps, page_size):
+    """The tensor-core path for steps of many tokens, bfloat16.  ``h_seqs``: one [T_b, W] input per sequence;
+    ``steps``: lists of how many tokens each sequence brings in that step."""
+    from mivi_v4_b200.parts.position import Rope
+    bf = torch.bfloat16
+    B = len(h_seqs)
+    H, dim, rd, vd, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    window, rot = (m.get("mask") or {}).get("size", 0), m.get("rot") or {"dims": 0}
+    per = [-(-x.shape[0] // page_size) for x in h_seqs]
+    n_pages = sum(per)
+    perm = torch.randperm(n_pages + 3, generator=torch.Generator().manual_seed(5))[:n_pages].tolist()
+    pool = torch.zeros(n_pages + 3, page_size * (rank + rd), dtype=bf, device=DEV)
+    rows_t, at = [], 0
+    for n in per:
+        rows_t.append(perm[at:at + n] + [0] * (max(per) - n))
+        at += n
+    table = i32(rows_t)
+    inv = Rope(rot["dims"], rot["base"], "half_split").rotary(DEV)[0] if rot["dims"] else None
+    c0, g0 = H * (dim + rd), H * (dim + rd) + rank + rd
+    w_kv = torch.cat([dev(p["uk"], bf), dev(p["uv"], bf)])
+    done = [0] * B
+    outs = [[] for _ in range(B)]
+    for lens in steps:
+        N = sum(lens)
+        proj = torch.cat([dev(h_seqs[b][done[b]:done[b] + lens[b]]) for b in range(B)])
+        pos = i32([done[b] + i for b in range(B) for i in range(lens[b])])
+        seq_of = i32([b for b in range(B) for _ in range(lens[b])])
+        cu = i32([sum(lens[:b]) for b in range(B + 1)])
+        starts = i32(done)
+        k.latent_prepare(proj, 0, c0, dev(p["dkv.norm"]), 1e-5, inv, pos, seq_of, table, pool, page_size, None, H, dim, rd,
+                         rank, rot["dims"])
+        q = torch.full((N, H, dim + rd), float("nan"), dtype=bf, device=DEV)
+        k.latent_query(proj, 0, inv, pos, q, H, dim, rd, rot["dims"])
+        rows = sum(done[b] + lens[b] - (max(0, done[b] - window + 1) if window else 0) for b in range(B))
+        c = torch.full((rows, rank), float("nan"), dtype=bf, device=DEV)
+        r = torch.full((rows, rd), float("nan"), dtype=bf, device=DEV)
+        k.latent_gather(pool, page_size, table, cu, starts, B, window, c, r)
+        kx = (c.float() @ w_kv.float().T).to(bf)
+        y = torch.full((N, H * vd), float("nan"), dtype=bf, device=DEV)
+        k.latent_attention_prefill(q, kx, H * dim, r, cu, starts, B, y, H, dim, rd, vd, m["scale"], window=window,
+                                   sinks=dev(p["sink"]), gate=proj[:, g0:g0 + H * vd])
+        at = 0
+        for b in range(B):
+            outs[b].append(y[at:at + lens[b]])
+            at += lens[b]
+            done[b] += lens[b]
+    return [torch.cat(o) for o in outs]
+
+
+LONG_SIZES = [(4, 32, 16, 48, 72, 64, 16, 500.0, 64), (2, 64, 32, 32, 64, 150, 32, 5e4, 16), (3, 8, 8, 16, 24, 33, 4, 50.0, 32),
+              (1, 128, 64, 128, 40, 0, 64, 1e6, 16), (5, 16, 0, 64, 16, 0, 0, 1.0, 8), (2, 24, 8, 80, 8, 1, 8, 10.0, 16)]
+
+
+@pytest.mark.parametrize("H,dim,rd,vd,rank,window,rot_dims,base,page", LONG_SIZES)
+def test_long_steps_on_the_tensor_cores_under_every_cut(H, dim, rd, vd, rank, window, rot_dims, base, page):
+    k, T = K(), 200
+    h, p, m, want = _latent_case(T, H, dim, rd, vd, rank, window, rot_dims, base, 0.3, seed=rank + H)
+    for cuts in ([T], [64, 64, 72], [100, 1, 99], [63, 65, 2, 70], [129, 71]):
+        got = _run_latent_long(k, [h], p, m, [[n] for n in cuts], page)[0]
+        close(got, want, 2e-2, f"cuts {cuts}")
+
+
+def test_long_steps_of_unequal_sequences_and_a_loud_key_at_the_window_edge():
+    """Three sequences of different lengths in the same steps, each against itself alone; then the loud key just
+    inside and just outside the window of the last query, in a whole prompt and in a prompt's second portion."""
+    k = K()
+    H, dim, rd, vd, rank = 2, 16, 16, 16, 16
+    cases = [_latent_case(T, H, dim, rd, vd, rank, 50, 16, 1e6, 0.4, seed=11) for T in (150, 31, 97)]
+    p, m = cases[0][1], cases[0][2]
+    got = _run_latent_long(k, [c[0] for c in cases], p, m, [[70, 31, 20], [80, 0, 77]], 16)
+    for b, c in enumerate(cases):
+        close(got[b], c[3], 2e-2, f"sequence {b} of three")
+    T = 140
+    for window, key, seen in ((40, 100, True), (40, 99, False), (0, 0, True), (140, 0, True), (139, 0, False), (64, 76, True),
+                              (64, 75, False)):
+        h, p, m, want = _latent_case(T, H, dim, rd, vd, rank, window, 16, 1e6, 0.5, seed=key + window, loud=(139, key))
+        for cuts in ([T], [90, 50], [120, 20]):
+            got = _run_latent_long(k, [h], p, m, [[n] for n in cuts], 16)[0]
+            close(got, want, 2e-2, f"window {window} loud key {key} cuts {cuts}")
+        c = P.rms_norm(h[key:key + 1, H * (dim + rd):H * (dim + rd) + rank], p["dkv.norm"], 1e-5)
+        v_key = (c @ p["uv"].T)[0] * torch.sigmoid(h[139, H * (dim + rd) + rank + rd:])
+        assert bool((want[139] - v_key).abs().max() < 0.05 * v_key.abs().max()) == seen, (window, key)
 
 
 def test_a_sink_takes_its_share_and_no_sink_is_plain_softmax():
