@@ -216,8 +216,11 @@ __device__ __forceinline__ void dl_commit() { asm volatile("cp.async.commit_grou
 template <int N> __device__ __forceinline__ void dl_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // One buffer of shared memory: [q: CHUNK dk | k: CHUNK dk | g: CHUNK dk | v: CHUNK DR_COLS | beta: CHUNK | k.q: CHUNK]
-template <int R>
-__global__ void __launch_bounds__(DR_COLS * DR_PART)
+// PART lanes share a column of the state (element i of it with lane i % PART): 8 for short keys; a whole warp from 64
+// key channels on, where a token then costs a lane a quarter of the work and a block holds 16 warps instead of 4, which
+// is what hides the latency of a chain that runs token after token.
+template <int R, int PART>
+__global__ void __launch_bounds__(DR_COLS * PART)
 delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __restrict__ v, int ldv,
                        float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu,
                        float* __restrict__ o, int n_heads, int kv_heads, int dk, int dv, int wide) {
@@ -225,7 +228,7 @@ delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __r
     extern __shared__ __align__(16) float dl_smem[];
     const int per = DL_CHUNK * (3 * dk + DR_COLS + 2);
     const int tile = blockIdx.x, h = blockIdx.y, sq = blockIdx.z;
-    const int tid = threadIdx.x, p = tid & (DR_PART - 1), jl = tid >> 3;
+    const int tid = threadIdx.x, p = tid & (PART - 1), jl = tid / PART;
     const int j = tile * DR_COLS + jl;
     const int row0 = cu[sq], len = cu[sq + 1] - row0;
     if (len <= 0) return;
@@ -236,7 +239,7 @@ delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __r
     float S[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int i = p + DR_PART * r;
+        const int i = p + PART * r;
         S[r] = (j < dv && i < dk) ? srow[i] : 0.f;
     }
     const int col0 = tile * DR_COLS;
@@ -251,7 +254,7 @@ delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __r
         float* ds = bs + DL_CHUNK;
         if (wide) {
             const int dk4 = dk >> 2;
-            for (int idx = tid; idx < nt * dk4; idx += DR_COLS * DR_PART) {
+            for (int idx = tid; idx < nt * dk4; idx += DR_COLS * PART) {
                 const int t = idx / dk4, i = (idx - t * dk4) << 2;
                 const float* src = prep + (size_t)(row0 + c0 + t) * ldp;
                 dl_copy16(qs + t * dk + i, src + (size_t)hk * dk + i);
@@ -259,7 +262,7 @@ delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __r
                 dl_copy16(gs + t * dk + i, src + 2 * qk + (size_t)h * dk + i);
             }
         } else {
-            for (int idx = tid; idx < nt * dk; idx += DR_COLS * DR_PART) {
+            for (int idx = tid; idx < nt * dk; idx += DR_COLS * PART) {
                 const int t = idx / dk, i = idx - t * dk;
                 const float* src = prep + (size_t)(row0 + c0 + t) * ldp;
                 dl_copy4(qs + idx, src + (size_t)hk * dk + i);
@@ -267,7 +270,7 @@ delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __r
                 dl_copy4(gs + idx, src + 2 * qk + (size_t)h * dk + i);
             }
         }
-        for (int idx = tid; idx < nt * DR_COLS; idx += DR_COLS * DR_PART) {
+        for (int idx = tid; idx < nt * DR_COLS; idx += DR_COLS * PART) {
             const int t = idx / DR_COLS, c = idx - t * DR_COLS;
             if (col0 + c < dv) dl_copy4(vs + idx, v + (size_t)(row0 + c0 + t) * ldv + (size_t)h * dv + col0 + c);
         }
@@ -305,7 +308,7 @@ delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __r
             float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
             for (int r = 0; r < R; r += 2) {
-                const int i0 = p + DR_PART * r, i1 = i0 + DR_PART;
+                const int i0 = p + PART * r, i1 = i0 + PART;
                 if (i0 < dk) {
                     S[r] *= gt[i0];
                     a0 = fmaf(S[r], kt[i0], a0);
@@ -318,16 +321,15 @@ delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __r
                 }
             }
             float said = a0 + a1, read = b0 + b1;
-            said += __shfl_xor_sync(0xffffffffu, said, 1);
-            read += __shfl_xor_sync(0xffffffffu, read, 1);
-            said += __shfl_xor_sync(0xffffffffu, said, 2);
-            read += __shfl_xor_sync(0xffffffffu, read, 2);
-            said += __shfl_xor_sync(0xffffffffu, said, 4);
-            read += __shfl_xor_sync(0xffffffffu, read, 4);
+#pragma unroll
+            for (int d = 1; d < PART; d <<= 1) {
+                said += __shfl_xor_sync(0xffffffffu, said, d);
+                read += __shfl_xor_sync(0xffffffffu, read, d);
+            }
             const float u = bs[t] * ((j < dv ? vs[t * DR_COLS + jl] : 0.f) - said);
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                const int i = p + DR_PART * r;
+                const int i = p + PART * r;
                 if (i < dk) S[r] = fmaf(kt[i], u, S[r]);
             }
             if (p == 0 && j < dv) o[(size_t)(row0 + c0 + t) * n_heads * dv + (size_t)h * dv + j] = fmaf(u, ds[t], read);
@@ -337,7 +339,7 @@ delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __r
     if (j < dv && mv_slot_ok(slots[sq])) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-            const int i = p + DR_PART * r;
+            const int i = p + PART * r;
             if (i < dk) srow[i] = S[r];
         }
     }
@@ -363,20 +365,21 @@ MV_API int mv_delta_scan_long(const float* q, int ldq, const float* k, int ldk, 
     const size_t smem = 2 * (size_t)DL_CHUNK * (3 * dk + DR_COLS + 2) * sizeof(float);
     // 16-byte copies: every row of q, k and g of a head starts on 16 bytes (ldp is a multiple of 4 floats)
     const int wide = dk % 4 == 0 && (((uintptr_t)prep) & 15) == 0;
-#define DL_LAUNCH(R)                                                                                                     \
+#define DL_LAUNCH(R, PART)                                                                                                   \
     do {                                                                                                                 \
         if (smem > 48 * 1024) {                                                                                          \
-            const cudaError_t e = cudaFuncSetAttribute(delta_scan_long_kernel<R>,                                        \
+            const cudaError_t e = cudaFuncSetAttribute(delta_scan_long_kernel<R, PART>,                                  \
                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
             if (e != cudaSuccess) return (int)e;                                                                         \
         }                                                                                                                \
-        mv_launch(delta_scan_long_kernel<R>, grid, DR_COLS * DR_PART, smem, stream, (const float*)prep, ldp, v, ldv, state, \
-                  slots, cu, o, n_heads, kv_heads, dk, dv, wide);                                                        \
+        mv_launch(delta_scan_long_kernel<R, PART>, grid, DR_COLS * PART, smem, stream, (const float*)prep, ldp, v, ldv,  \
+                  state, slots, cu, o, n_heads, kv_heads, dk, dv, wide);                                                 \
     } while (0)
-    if (dk <= 32) DL_LAUNCH(4);
-    else if (dk <= 64) DL_LAUNCH(8);
-    else if (dk <= 128) DL_LAUNCH(16);
-    else DL_LAUNCH(32);
+    if (dk <= 32) DL_LAUNCH(4, 8);
+    else if (dk < 64) DL_LAUNCH(8, 8);
+    else if (dk == 64) DL_LAUNCH(2, 32);
+    else if (dk <= 128) DL_LAUNCH(4, 32);
+    else DL_LAUNCH(8, 32);
 #undef DL_LAUNCH
     return mv_launch_status();
 }

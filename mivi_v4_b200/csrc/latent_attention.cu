@@ -190,6 +190,7 @@ MV_API int mv_head_product(const float* x, long long ldx, int hx, const void* w,
 // so the sink counts once and has no value.
 #define LA_HEADS 8
 #define LA_KEYS 32
+#define LA_AHEAD 5             // 16-byte copies a thread has on their way at a time
 #define LA_MAX_OUT 32          // output columns a lane (the template's R) at most: rank <= 1024
 
 template <typename T, int R>
@@ -200,7 +201,7 @@ latent_attention_kernel(const float* __restrict__ qa, const T* __restrict__ pool
                         const float* __restrict__ sinks, float* __restrict__ out, int nh, int rank, int rot, float scale,
                         int window, int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
     mv_pdl_begin();
-    extern __shared__ float la_smem[];
+    extern __shared__ __align__(16) float la_smem[];
     const int w = rank + rot;
     const int wp = w | 1;                                       // odd row pitch: a lane a row without bank conflicts
     float* qs = la_smem;                                        // [LA_HEADS][w]
@@ -211,6 +212,8 @@ latent_attention_kernel(const float* __restrict__ qa, const T* __restrict__ pool
     const int pos = positions[n];
     const int* table = page_table + (size_t)seq_of[n] * table_stride;
     const int page_mask = (1 << page_shift) - 1;
+    // rows of the cache start on 16 bytes and are whole 16-byte pieces
+    const bool wide = (w * sizeof(T)) % 16 == 0 && (page_stride * sizeof(T)) % 16 == 0 && ((uintptr_t)pool & 15) == 0;
     for (int e = threadIdx.x; e < heads * w; e += blockDim.x) qs[e] = qa[((size_t)n * nh + h0) * w + e];
     int j_lo = window > 0 ? max(0, pos - window + 1) : 0;
     int j_hi = pos;
@@ -232,11 +235,43 @@ latent_attention_kernel(const float* __restrict__ qa, const T* __restrict__ pool
     for (int j0 = j_lo; j0 <= j_hi; j0 += LA_KEYS) {
         const int nk = min(LA_KEYS, j_hi - j0 + 1);
         __syncthreads();
-        for (int e = threadIdx.x; e < nk * w; e += blockDim.x) {
-            const int r = e / w, c = e - r * w;
-            const int j = j0 + r;
-            const int page = mv_read_page(table[j >> page_shift]);
-            ks[r * wp + c] = mv_to_f32(pool[(size_t)page * page_stride + (size_t)(j & page_mask) * w + c]);
+        if (wide) {
+            // 16 bytes a copy, LA_AHEAD of them on their way before the first is unpacked: a thread that waited for
+            // every element by itself spent the tile waiting
+            constexpr int V = 16 / (int)sizeof(T);
+            const int cpr = w / V, total = nk * cpr;
+            for (int e0 = threadIdx.x; e0 < total; e0 += LA_AHEAD * LA_HEADS * 32) {
+                uint4 got[LA_AHEAD];
+#pragma unroll
+                for (int u = 0; u < LA_AHEAD; ++u) {
+                    const int e = e0 + u * LA_HEADS * 32;
+                    if (e < total) {
+                        const int r = e / cpr, c = e - r * cpr;
+                        const int j = j0 + r;
+                        const int page = mv_read_page(table[j >> page_shift]);
+                        got[u] = *reinterpret_cast<const uint4*>(pool + (size_t)page * page_stride +
+                                                                 (size_t)(j & page_mask) * w + c * V);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < LA_AHEAD; ++u) {
+                    const int e = e0 + u * LA_HEADS * 32;
+                    if (e < total) {
+                        const int r = e / cpr, c = e - r * cpr;
+                        float f[V];
+                        mv_unpack16(got[u], f, (const T*)nullptr);
+#pragma unroll
+                        for (int i = 0; i < V; ++i) ks[r * wp + c * V + i] = f[i];
+                    }
+                }
+            }
+        } else {
+            for (int e = threadIdx.x; e < nk * w; e += blockDim.x) {
+                const int r = e / w, c = e - r * w;
+                const int j = j0 + r;
+                const int page = mv_read_page(table[j >> page_shift]);
+                ks[r * wp + c] = mv_to_f32(pool[(size_t)page * page_stride + (size_t)(j & page_mask) * w + c]);
+            }
         }
         __syncthreads();
         if (!active) continue;
@@ -244,7 +279,19 @@ latent_attention_kernel(const float* __restrict__ qa, const T* __restrict__ pool
         if (lane < nk) {
             const float* kr = ks + lane * wp;
             float d = 0.f;
-            for (int c = 0; c < w; ++c) d = fmaf(q[c], kr[c], d);
+            int c = 0;
+            if ((w & 3) == 0) {                     // q four elements a load (a row of qs then starts on 16 bytes)
+                float d1 = 0.f, d2 = 0.f, d3 = 0.f;
+                for (; c < w; c += 4) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(q + c);
+                    d = fmaf(q4.x, kr[c], d);
+                    d1 = fmaf(q4.y, kr[c + 1], d1);
+                    d2 = fmaf(q4.z, kr[c + 2], d2);
+                    d3 = fmaf(q4.w, kr[c + 3], d3);
+                }
+                d = (d + d1) + (d2 + d3);
+            }
+            for (; c < w; ++c) d = fmaf(q[c], kr[c], d);
             s = d * scale;
         }
         const float m_new = fmaxf(m, mv_warp_max(s));

@@ -306,8 +306,8 @@ def test_long_steps_of_unequal_sequences_and_a_loud_key_at_the_window_edge():
     cases = [_latent_case(T, H, dim, rd, vd, rank, 50, 16, 1e6, 0.4, seed=11) for T in (150, 31, 97)]
     p, m = cases[0][1], cases[0][2]
     got = _run_latent_long(k, [c[0] for c in cases], p, m, [[70, 31, 20], [80, 0, 77]], 16)
-    for b, c in enumerate(cases):
-        close(got[b], c[3], 2e-2, f"sequence {b} of three")
+    for b, c in enumerate(cases):                     # every case drew weights of its own: the first one's serve all
+        close(got[b], P.latent_attention(c[0], p, m, 1e-5), 2e-2, f"sequence {b} of three")
     T = 140
     for window, key, seen in ((40, 100, True), (40, 99, False), (0, 0, True), (140, 0, True), (139, 0, False), (64, 76, True),
                               (64, 75, False)):
