@@ -215,6 +215,47 @@ __device__ __forceinline__ void dl_copy16(float* smem, const float* gmem) {
 __device__ __forceinline__ void dl_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void dl_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// The rows of q, k and g, DR_COLS columns of v, beta and k.q of up to DL_CHUNK tokens from token c0 of a sequence on
+// their way into one buffer of shared memory.
+__device__ __forceinline__ void dl_stage(float* buf, const float* __restrict__ prep, int ldp, const float* __restrict__ v,
+                                         int ldv, int row0, int c0, int len, int h, int hk, int qk, int n_heads, int dk,
+                                         int dv, int col0, int wide, int tid, int nthreads) {
+        const int nt = min(DL_CHUNK, len - c0);
+        float* qs = buf;
+        float* ks = qs + DL_CHUNK * dk;
+        float* gs = ks + DL_CHUNK * dk;
+        float* vs = gs + DL_CHUNK * dk;
+        float* bs = vs + DL_CHUNK * DR_COLS;
+        float* ds = bs + DL_CHUNK;
+        if (wide) {
+            const int dk4 = dk >> 2;
+            for (int idx = tid; idx < nt * dk4; idx += nthreads) {
+                const int t = idx / dk4, i = (idx - t * dk4) << 2;
+                const float* src = prep + (size_t)(row0 + c0 + t) * ldp;
+                dl_copy16(qs + t * dk + i, src + (size_t)hk * dk + i);
+                dl_copy16(ks + t * dk + i, src + qk + (size_t)hk * dk + i);
+                dl_copy16(gs + t * dk + i, src + 2 * qk + (size_t)h * dk + i);
+            }
+        } else {
+            for (int idx = tid; idx < nt * dk; idx += nthreads) {
+                const int t = idx / dk, i = idx - t * dk;
+                const float* src = prep + (size_t)(row0 + c0 + t) * ldp;
+                dl_copy4(qs + idx, src + (size_t)hk * dk + i);
+                dl_copy4(ks + idx, src + qk + (size_t)hk * dk + i);
+                dl_copy4(gs + idx, src + 2 * qk + (size_t)h * dk + i);
+            }
+        }
+        for (int idx = tid; idx < nt * DR_COLS; idx += nthreads) {
+            const int t = idx / DR_COLS, c = idx - t * DR_COLS;
+            if (col0 + c < dv) dl_copy4(vs + idx, v + (size_t)(row0 + c0 + t) * ldv + (size_t)h * dv + col0 + c);
+        }
+        if (tid < nt) {
+            const float* src = prep + (size_t)(row0 + c0 + tid) * ldp + 2 * qk + (size_t)n_heads * dk;
+            dl_copy4(bs + tid, src + h);
+            dl_copy4(ds + tid, src + n_heads + hk);
+        }
+    }
+
 // One buffer of shared memory: [q: CHUNK dk | k: CHUNK dk | g: CHUNK dk | v: CHUNK DR_COLS | beta: CHUNK | k.q: CHUNK]
 // PART lanes share a column of the state (element i of it with lane i % PART): 8 for short keys; a whole warp from 64
 // key channels on, where a token then costs a lane a quarter of the work and a block holds 16 warps instead of 4, which
@@ -224,7 +265,9 @@ __global__ void __launch_bounds__(DR_COLS * PART)
 delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __restrict__ v, int ldv,
                        float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu,
                        float* __restrict__ o, int n_heads, int kv_heads, int dk, int dv, int wide) {
-    mv_pdl_begin();
+    // The successor may not start early here: its blocks would sit on the multiprocessors for the whole walk, and with
+    // them there the walk was measured 1.75 times slower.  It is let go when the last token is done.
+    mv_pdl_wait();
     extern __shared__ __align__(16) float dl_smem[];
     const int per = DL_CHUNK * (3 * dk + DR_COLS + 2);
     const int tile = blockIdx.x, h = blockIdx.y, sq = blockIdx.z;
@@ -245,40 +288,7 @@ delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __r
     const int col0 = tile * DR_COLS;
 
     auto stage = [&](int c0, float* buf) {
-        const int nt = min(DL_CHUNK, len - c0);
-        float* qs = buf;
-        float* ks = qs + DL_CHUNK * dk;
-        float* gs = ks + DL_CHUNK * dk;
-        float* vs = gs + DL_CHUNK * dk;
-        float* bs = vs + DL_CHUNK * DR_COLS;
-        float* ds = bs + DL_CHUNK;
-        if (wide) {
-            const int dk4 = dk >> 2;
-            for (int idx = tid; idx < nt * dk4; idx += DR_COLS * PART) {
-                const int t = idx / dk4, i = (idx - t * dk4) << 2;
-                const float* src = prep + (size_t)(row0 + c0 + t) * ldp;
-                dl_copy16(qs + t * dk + i, src + (size_t)hk * dk + i);
-                dl_copy16(ks + t * dk + i, src + qk + (size_t)hk * dk + i);
-                dl_copy16(gs + t * dk + i, src + 2 * qk + (size_t)h * dk + i);
-            }
-        } else {
-            for (int idx = tid; idx < nt * dk; idx += DR_COLS * PART) {
-                const int t = idx / dk, i = idx - t * dk;
-                const float* src = prep + (size_t)(row0 + c0 + t) * ldp;
-                dl_copy4(qs + idx, src + (size_t)hk * dk + i);
-                dl_copy4(ks + idx, src + qk + (size_t)hk * dk + i);
-                dl_copy4(gs + idx, src + 2 * qk + (size_t)h * dk + i);
-            }
-        }
-        for (int idx = tid; idx < nt * DR_COLS; idx += DR_COLS * PART) {
-            const int t = idx / DR_COLS, c = idx - t * DR_COLS;
-            if (col0 + c < dv) dl_copy4(vs + idx, v + (size_t)(row0 + c0 + t) * ldv + (size_t)h * dv + col0 + c);
-        }
-        if (tid < nt) {
-            const float* src = prep + (size_t)(row0 + c0 + tid) * ldp + 2 * qk + (size_t)n_heads * dk;
-            dl_copy4(bs + tid, src + h);
-            dl_copy4(ds + tid, src + n_heads + hk);
-        }
+        dl_stage(buf, prep, ldp, v, ldv, row0, c0, len, h, hk, qk, n_heads, dk, dv, col0, wide, tid, DR_COLS * PART);
     };
 
     stage(0, dl_smem);
@@ -336,11 +346,124 @@ delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __r
         }
         __syncthreads();
     }
+    mv_pdl_launch_dependents();
     if (j < dv && mv_slot_ok(slots[sq])) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const int i = p + PART * r;
             if (i < dk) srow[i] = S[r];
+        }
+    }
+}
+
+// From 64 key channels on: a warp carries TWO columns of the state, lane l the channels l, l + 32, ...  A token's q, k and
+// g are read once for both columns, and the four sums of a token (what the state says for k and what it reads out
+// for q, in each column) are folded while they are added up: lanes exchange the half they do not keep, so 4 + 2 + 1
+// values go round instead of 4 x 5, and lanes 0, 8, 16 and 24 end up with one whole sum each.
+template <int R>
+__global__ void __launch_bounds__(DR_COLS * 16)
+delta_scan_warp_kernel(const float* __restrict__ prep, int ldp, const float* __restrict__ v, int ldv,
+                       float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu,
+                       float* __restrict__ o, int n_heads, int kv_heads, int dk, int dv, int wide) {
+    // The successor may not start early here: its blocks would sit on the multiprocessors for the whole walk, and with
+    // them there the walk was measured 1.75 times slower.  It is let go when the last token is done.
+    mv_pdl_wait();
+    extern __shared__ __align__(16) float dl_smem[];
+    const int per = DL_CHUNK * (3 * dk + DR_COLS + 2);
+    const int tile = blockIdx.x, h = blockIdx.y, sq = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, jl = (tid >> 5) * 2;
+    const int col0 = tile * DR_COLS;
+    const int j0 = col0 + jl, j1 = j0 + 1;
+    const int row0 = cu[sq], len = cu[sq + 1] - row0;
+    if (len <= 0) return;
+    const int hk = h / (n_heads / kv_heads);
+    const int qk = kv_heads * dk;
+    const int slot = mv_read_slot(slots[sq]);
+    float* srow0 = state + (((size_t)slot * n_heads + h) * dv + (j0 < dv ? j0 : 0)) * dk;
+    float* srow1 = state + (((size_t)slot * n_heads + h) * dv + (j1 < dv ? j1 : 0)) * dk;
+    float S0[R], S1[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int i = lane + 32 * r;
+        S0[r] = (j0 < dv && i < dk) ? srow0[i] : 0.f;
+        S1[r] = (j1 < dv && i < dk) ? srow1[i] : 0.f;
+    }
+    const bool hi16 = lane & 16, hi8 = lane & 8;
+
+    dl_stage(dl_smem, prep, ldp, v, ldv, row0, 0, len, h, hk, qk, n_heads, dk, dv, col0, wide, tid, DR_COLS * 16);
+    dl_commit();
+    int which = 0;
+    for (int c0 = 0; c0 < len; c0 += DL_CHUNK, which ^= 1) {
+        float* buf = dl_smem + which * per;
+        if (c0 + DL_CHUNK < len) {
+            dl_stage(dl_smem + (which ^ 1) * per, prep, ldp, v, ldv, row0, c0 + DL_CHUNK, len, h, hk, qk, n_heads, dk, dv,
+                     col0, wide, tid, DR_COLS * 16);
+            dl_commit();
+            dl_wait<1>();
+        } else {
+            dl_wait<0>();
+        }
+        __syncthreads();
+        const int nt = min(DL_CHUNK, len - c0);
+        const float* qs = buf;
+        const float* ks = qs + DL_CHUNK * dk;
+        const float* gs = ks + DL_CHUNK * dk;
+        const float* vs = gs + DL_CHUNK * dk;
+        const float* bs = vs + DL_CHUNK * DR_COLS;
+        const float* ds = bs + DL_CHUNK;
+        for (int t = 0; t < nt; ++t) {
+            const float* qt = qs + t * dk;
+            const float* kt = ks + t * dk;
+            const float* gt = gs + t * dk;
+            float kr[R];
+            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int i = lane + 32 * r;
+                kr[r] = 0.f;
+                if (i < dk) {
+                    const float g = gt[i], q = qt[i];
+                    kr[r] = kt[i];
+                    S0[r] *= g;
+                    S1[r] *= g;
+                    a0 = fmaf(S0[r], kr[r], a0);
+                    a1 = fmaf(S1[r], kr[r], a1);
+                    b0 = fmaf(S0[r], q, b0);
+                    b1 = fmaf(S1[r], q, b1);
+                }
+            }
+            // lanes 0..15 keep what the state says for k, lanes 16..31 what it reads for q; then lanes with bit 3 clear
+            // keep the first column and the others the second
+            const float x0 = (hi16 ? b0 : a0) + __shfl_xor_sync(0xffffffffu, hi16 ? a0 : b0, 16);
+            const float x1 = (hi16 ? b1 : a1) + __shfl_xor_sync(0xffffffffu, hi16 ? a1 : b1, 16);
+            float y = (hi8 ? x1 : x0) + __shfl_xor_sync(0xffffffffu, hi8 ? x0 : x1, 8);
+            y += __shfl_xor_sync(0xffffffffu, y, 4);
+            y += __shfl_xor_sync(0xffffffffu, y, 2);
+            y += __shfl_xor_sync(0xffffffffu, y, 1);
+            const float said0 = __shfl_sync(0xffffffffu, y, 0), said1 = __shfl_sync(0xffffffffu, y, 8);
+            const float beta = bs[t];
+            const float u0 = beta * ((j0 < dv ? vs[t * DR_COLS + jl] : 0.f) - said0);
+            const float u1 = beta * ((j1 < dv ? vs[t * DR_COLS + jl + 1] : 0.f) - said1);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                S0[r] = fmaf(kr[r], u0, S0[r]);
+                S1[r] = fmaf(kr[r], u1, S1[r]);
+            }
+            float* orow = o + (size_t)(row0 + c0 + t) * n_heads * dv + (size_t)h * dv;
+            if (lane == 16 && j0 < dv) orow[j0] = fmaf(u0, ds[t], y);
+            if (lane == 24 && j1 < dv) orow[j1] = fmaf(u1, ds[t], y);
+        }
+        __syncthreads();
+    }
+    mv_pdl_launch_dependents();
+    if (mv_slot_ok(slots[sq])) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int i = lane + 32 * r;
+            if (i < dk) {
+                if (j0 < dv) srow0[i] = S0[r];
+                if (j1 < dv) srow1[i] = S1[r];
+            }
         }
     }
 }
@@ -375,11 +498,22 @@ MV_API int mv_delta_scan_long(const float* q, int ldq, const float* k, int ldk, 
         mv_launch(delta_scan_long_kernel<R, PART>, grid, DR_COLS * PART, smem, stream, (const float*)prep, ldp, v, ldv,  \
                   state, slots, cu, o, n_heads, kv_heads, dk, dv, wide);                                                 \
     } while (0)
+#define DW_LAUNCH(R)                                                                                                     \
+    do {                                                                                                                 \
+        if (smem > 48 * 1024) {                                                                                          \
+            const cudaError_t e = cudaFuncSetAttribute(delta_scan_warp_kernel<R>,                                        \
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
+            if (e != cudaSuccess) return (int)e;                                                                         \
+        }                                                                                                                \
+        mv_launch(delta_scan_warp_kernel<R>, grid, DR_COLS * 16, smem, stream, (const float*)prep, ldp, v, ldv, state,  \
+                  slots, cu, o, n_heads, kv_heads, dk, dv, wide);                                                        \
+    } while (0)
     if (dk <= 32) DL_LAUNCH(4, 8);
     else if (dk < 64) DL_LAUNCH(8, 8);
-    else if (dk == 64) DL_LAUNCH(2, 32);
-    else if (dk <= 128) DL_LAUNCH(4, 32);
-    else DL_LAUNCH(8, 32);
+    else if (dk == 64) DW_LAUNCH(2);
+    else if (dk <= 128) DW_LAUNCH(4);
+    else DW_LAUNCH(8);
+#undef DW_LAUNCH
 #undef DL_LAUNCH
     return mv_launch_status();
 }

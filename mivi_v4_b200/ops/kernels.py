@@ -1124,7 +1124,7 @@ def head_product(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, nh: int, n_i
 
 
 # a (token, head tile) whose keys would keep one block busy for more than this many of them is cut into shares
-LATENT_SPLIT_KEYS = 256
+LATENT_SPLIT_KEYS = 128
 LATENT_MAX_SPLITS = 32
 
 
