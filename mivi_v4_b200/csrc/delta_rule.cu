@@ -265,9 +265,7 @@ __global__ void __launch_bounds__(DR_COLS * PART)
 delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __restrict__ v, int ldv,
                        float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu,
                        float* __restrict__ o, int n_heads, int kv_heads, int dk, int dv, int wide) {
-    // The successor may not start early here: its blocks would sit on the multiprocessors for the whole walk, and with
-    // them there the walk was measured 1.75 times slower.  It is let go when the last token is done.
-    mv_pdl_wait();
+    mv_pdl_wait();                          // the successor is let go when the last token is done
     extern __shared__ __align__(16) float dl_smem[];
     const int per = DL_CHUNK * (3 * dk + DR_COLS + 2);
     const int tile = blockIdx.x, h = blockIdx.y, sq = blockIdx.z;
@@ -365,9 +363,7 @@ __global__ void __launch_bounds__(DR_COLS * 16)
 delta_scan_warp_kernel(const float* __restrict__ prep, int ldp, const float* __restrict__ v, int ldv,
                        float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu,
                        float* __restrict__ o, int n_heads, int kv_heads, int dk, int dv, int wide) {
-    // The successor may not start early here: its blocks would sit on the multiprocessors for the whole walk, and with
-    // them there the walk was measured 1.75 times slower.  It is let go when the last token is done.
-    mv_pdl_wait();
+    mv_pdl_wait();                          // the successor is let go when the last token is done
     extern __shared__ __align__(16) float dl_smem[];
     const int per = DL_CHUNK * (3 * dk + DR_COLS + 2);
     const int tile = blockIdx.x, h = blockIdx.y, sq = blockIdx.z;
@@ -484,6 +480,10 @@ MV_API int mv_delta_scan_long(const float* q, int ldq, const float* k, int ldk, 
     const int ldp = mv_delta_prep_width(n_heads, kv_heads, dk);
     mv_launch(delta_prepare_kernel, N, 256, 0, stream, q, ldq, k, ldk, b, ldb, a, lda, dt_bias, a_log, q_scale, norm_eps, prep,
               ldp, n_heads, kv_heads, dk);
+    // The walk is launched as an ordinary successor, not a programmatic one.  Started while the preparing kernel's blocks
+    // still hold the multiprocessors, its few blocks (one sequence of 16 heads x 128 values: 128) went where room came
+    // up first, several to a multiprocessor, and the walk, bound by what ONE multiprocessor issues, took 1.75 times as
+    // long as when they are dealt out over an idle device (measured: 1.26 ms against 0.72 for 2,048 tokens).
     const dim3 grid((dv + DR_COLS - 1) / DR_COLS, n_heads, n_seqs);
     const size_t smem = 2 * (size_t)DL_CHUNK * (3 * dk + DR_COLS + 2) * sizeof(float);
     // 16-byte copies: every row of q, k and g of a head starts on 16 bytes (ldp is a multiple of 4 floats)
@@ -495,8 +495,9 @@ MV_API int mv_delta_scan_long(const float* q, int ldq, const float* k, int ldk, 
                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
             if (e != cudaSuccess) return (int)e;                                                                         \
         }                                                                                                                \
-        mv_launch(delta_scan_long_kernel<R, PART>, grid, DR_COLS * PART, smem, stream, (const float*)prep, ldp, v, ldv,  \
-                  state, slots, cu, o, n_heads, kv_heads, dk, dv, wide);                                                 \
+        delta_scan_long_kernel<R, PART><<<grid, DR_COLS * PART, smem, stream>>>((const float*)prep, ldp, v, ldv, state,  \
+                                                                                slots, cu, o, n_heads, kv_heads, dk, dv, \
+                                                                                wide);                                   \
     } while (0)
 #define DW_LAUNCH(R)                                                                                                     \
     do {                                                                                                                 \
@@ -505,8 +506,8 @@ MV_API int mv_delta_scan_long(const float* q, int ldq, const float* k, int ldk, 
                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
             if (e != cudaSuccess) return (int)e;                                                                         \
         }                                                                                                                \
-        mv_launch(delta_scan_warp_kernel<R>, grid, DR_COLS * 16, smem, stream, (const float*)prep, ldp, v, ldv, state,  \
-                  slots, cu, o, n_heads, kv_heads, dk, dv, wide);                                                        \
+        delta_scan_warp_kernel<R><<<grid, DR_COLS * 16, smem, stream>>>((const float*)prep, ldp, v, ldv, state, slots,  \
+                                                                        cu, o, n_heads, kv_heads, dk, dv, wide);         \
     } while (0)
     if (dk <= 32) DL_LAUNCH(4, 8);
     else if (dk < 64) DL_LAUNCH(8, 8);
