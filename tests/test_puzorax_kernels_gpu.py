@@ -79,7 +79,8 @@ def _run_delta(k, case, cuts, H, KV, dk, dv, state, slot, ws):
     return torch.cat(outs)
 
 
-@pytest.mark.parametrize("H,KV,dk,dv", [(4, 2, 16, 8), (1, 1, 20, 12), (2, 1, 72, 40), (1, 1, 136, 17), (3, 3, 5, 33)])
+@pytest.mark.parametrize("H,KV,dk,dv", [(4, 2, 16, 8), (1, 1, 20, 12), (2, 1, 72, 40), (1, 1, 136, 17), (3, 3, 5, 33),
+                                        (2, 1, 64, 32), (2, 2, 128, 18), (1, 1, 256, 16), (2, 1, 48, 16)])
 def test_delta_rule_under_every_cut_token_by_token_and_in_long_steps(H, KV, dk, dv):
     k, T = K(), 61
     case, want = _delta_case(T, H, KV, dk, dv, seed=dk)
