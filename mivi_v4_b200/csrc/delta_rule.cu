@@ -257,9 +257,9 @@ __device__ __forceinline__ void dl_stage(float* buf, const float* __restrict__ p
     }
 
 // One buffer of shared memory: [q: CHUNK dk | k: CHUNK dk | g: CHUNK dk | v: CHUNK DR_COLS | beta: CHUNK | k.q: CHUNK]
-// PART lanes share a column of the state (element i of it with lane i % PART): 8 for short keys; a whole warp from 64
-// key channels on, where a token then costs a lane a quarter of the work and a block holds 16 warps instead of 4, which
-// is what hides the latency of a chain that runs token after token.
+// PART lanes share a column of the state (element i of it with lane i % PART).  Keys under 64 channels run here with 8
+// lanes a column; from 64 channels on delta_scan_warp_kernel below takes over.  (A whole warp a column, 16 warps a
+// block, was measured issue-bound: 740 us for 2,048 tokens of 128 x 128 against 696 for the kernel below.)
 template <int R, int PART>
 __global__ void __launch_bounds__(DR_COLS * PART)
 delta_scan_long_kernel(const float* __restrict__ prep, int ldp, const float* __restrict__ v, int ldv,
