@@ -1,2 +1,2 @@
 """One file per architecture; importing this package registers them all."""
-from . import lfm2, puzorax, tevirax, votavik  # noqa: F401
+from . import lfm2, puzorax, ropelix, tevirax, votavik  # noqa: F401

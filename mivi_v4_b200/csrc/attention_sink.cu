@@ -15,6 +15,12 @@
 //     by longer vectors);
 //   * a chunked mask: query i reads key j <= i only if both lie in the same chunk of `chunk` positions,
 //     counted from the sequence's position 0.
+//   * a distance bias: r1_h ln(1 + r2_h (i - j)) is taken off the score of query i and key j, two numbers a head;
+//   * values that are the keys (the first dv elements of a key row): a page then holds key rows only;
+//   * a gate per token and ELEMENT of the concatenated heads instead of one per head;
+//   * every query head's weights applied to the values of EVERY kv head (32-bit results [token][head][kv head][dv]),
+//     from which mv_mix_heads forms  out_h = sum_g talk[h][g] O[g][kv head of h]: softmax weights mixed between the
+//     heads after the softmax, each head reading the values of its own kv head.
 // Each is a parameter (0 or null turns it off).
 //
 // Cache layout of one layer's page: [kv head][row][dk] keys, then [kv head][row][dv] values; with
@@ -157,7 +163,8 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
                       const int* __restrict__ positions, const int* __restrict__ seq_of,
                       const float* __restrict__ sinks, const float* __restrict__ gate, int ld_gate,
                       T* __restrict__ o, int N, int nh, int nkv, int dk, int dv, float scale, float cap, int window,
-                      int keep_first, int chunk) {
+                      int keep_first, int chunk, const float* __restrict__ r1, const float* __restrict__ r2, int v_in_k,
+                      int gate_wide, float* __restrict__ o_all) {
     mv_pdl_begin();
     extern __shared__ __align__(16) float as_smem[];
     float* qs = as_smem;                            // [GT][dk]
@@ -166,13 +173,18 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
     float* part_l = part_m + AS_WARPS * GT;
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = nh / nkv, tiles = (G + GT - 1) / GT;
-    const int n = blockIdx.x / (nkv * tiles), rest = blockIdx.x - n * nkv * tiles;
+    // with o_all a block is one of nkv that share (token, kv head, tile): each applies the weights to another kv head's values
+    const int vm = o_all ? nkv : 1;
+    const int bid = blockIdx.x / vm, vg_all = blockIdx.x - bid * vm;
+    const int n = bid / (nkv * tiles), rest = bid - n * nkv * tiles;
     const int g = rest / tiles, h0 = g * G + (rest - g * tiles) * GT;        // the tile's first query head
+    const int vg = o_all ? vg_all : g;                                       // the kv head whose values are read
     const int n_heads = min(GT, (g + 1) * G - h0);
     const int pos = positions[n];
     const int page_size = 1 << page_shift;
     const int* table = page_table + (size_t)seq_of[n] * table_stride;
-    const size_t v_base = (size_t)nkv * page_size * dk;
+    const size_t v_base = v_in_k ? 0 : (size_t)nkv * page_size * dk;
+    const int v_ld = v_in_k ? dk : dv;
 
     for (int idx = threadIdx.x; idx < GT * dk; idx += AS_WARPS * 32) {
         const int i = idx / dk, d = idx - i * dk;
@@ -208,7 +220,7 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
             const T* pbase = pool + (size_t)page * page_stride;
             const size_t r = (size_t)g * page_size + (t & (page_size - 1));
             const T* krow = pbase + r * dk;
-            vaddr = (unsigned long long)(pbase + v_base + r * dv);
+            vaddr = (unsigned long long)(pbase + v_base + ((size_t)vg * page_size + (t & (page_size - 1))) * v_ld);
             float dot[GT];
 #pragma unroll
             for (int i = 0; i < GT; ++i) dot[i] = 0.f;
@@ -238,6 +250,7 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
 #pragma unroll
             for (int i = 0; i < GT; ++i) {
                 s[i] = dot[i] * scale;
+                if (r1 && i < n_heads) s[i] -= r1[h0 + i] * log1pf(r2[h0 + i] * (float)(pos - t));
                 if (cap > 0.f) {
                     if (sizeof(T) == 2) {
                         // a bfloat16 run: tanh(x) = (1 - e^-2|x|) / (1 + e^-2|x|) with the fast exponential, as in the
@@ -312,19 +325,26 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
             v = fmaf(part_acc[(w * GT + i) * dv + d], wgt, v);
         }
         float mul = 1.0f / L;
-        if (gate) mul *= 1.0f / (1.0f + expf(-gate[(size_t)n * ld_gate + h0 + i]));
-        o[((size_t)n * nh + h0 + i) * dv + d] = mv_from_f32<T>(v * mul);
+        if (gate) mul *= 1.0f / (1.0f + expf(-gate[(size_t)n * ld_gate + (gate_wide ? (size_t)(h0 + i) * dv + d : (size_t)(h0 + i))]));
+        if (o_all)
+            o_all[(((size_t)n * nh + h0 + i) * nkv + vg) * dv + d] = v * mul;
+        else
+            o[((size_t)n * nh + h0 + i) * dv + d] = mv_from_f32<T>(v * mul);
     }
 }
 
-// head_tile: see below.  q [N, nh * dk]; o [N, nh * dv]; sinks [nh] or null; gate: 32-bit logits, gate[n * ld_gate + h], or null.
+// head_tile: see below.  q [N, nh * dk]; o [N, nh * dv]; sinks [nh] or null; gate: 32-bit logits, gate[n * ld_gate + h]
+// (with gate_wide gate[n * ld_gate + h * dv + d]), or null; r1, r2 [nh] or null; v_in_k: the values are the keys' first dv
+// elements; o_all: 32-bit [N, nh, nkv, dv] or null (then o is not written).
 MV_API int mv_attention_sink(const void* q, const void* pool, long long page_stride, const int* page_table,
                              int table_stride, int page_size, const int* positions, const int* seq_of,
                              const float* sinks, const float* gate, int ld_gate, void* o, int dtype, int N, int nh,
                              int nkv, int dk, int dv, float scale, float cap, int window, int keep_first,
-                             int head_tile, int chunk, cudaStream_t stream) {
+                             int head_tile, int chunk, const float* r1, const float* r2, int v_in_k, int gate_wide,
+                             float* o_all, cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (dk < 1 || dk > AS_MAX_DIM || dv < 1 || dv > AS_MAX_DIM || nkv < 1 || nh % nkv || (page_size & (page_size - 1)))
+    if (dk < 1 || dk > AS_MAX_DIM || dv < 1 || dv > AS_MAX_DIM || nkv < 1 || nh % nkv || (page_size & (page_size - 1)) ||
+        (v_in_k && dv > dk) || (r1 && !r2))
         return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
@@ -335,14 +355,14 @@ MV_API int mv_attention_sink(const void* q, const void* pool, long long page_str
     // come from L2 anyway), so tiles are chosen only for steps of thousands of (token, head) pairs.
     int gt = head_tile > 0 ? head_tile : ((long long)N * nh >= 4096 && G >= 2 ? 2 : 1);
     if (gt != 1 && gt != 2 && gt != 4) return (int)cudaErrorInvalidValue;
-    const unsigned blocks = (unsigned)((long long)N * nkv * ((G + gt - 1) / gt));
+    const unsigned blocks = (unsigned)((long long)N * nkv * ((G + gt - 1) / gt) * (o_all ? nkv : 1));
     const int esize = dtype == MV_DT_BF16 ? 2 : 4;
     const bool vec = dk % 8 == 0 && ((uintptr_t)pool % 16) == 0 && (page_stride * esize) % 16 == 0;
     const size_t smem = sizeof(float) * ((size_t)gt * dk + (size_t)AS_WARPS * gt * (dv + 2));
 #define AS_LAUNCH(T, V, GTV)                                                                                         \
     mv_launch(attention_sink_kernel<T, V, GTV>, blocks, AS_WARPS * 32, smem, stream, (const T*)q, (const T*)pool,    \
               page_stride, page_table, table_stride, page_shift, positions, seq_of, sinks, gate, ld_gate, (T*)o, N,  \
-              nh, nkv, dk, dv, scale, cap, window, keep_first, chunk)
+              nh, nkv, dk, dv, scale, cap, window, keep_first, chunk, r1, r2, v_in_k, gate_wide, o_all)
 #define AS_PICK(T, V)                                                                                                \
     do {                                                                                                             \
         if (gt == 4) AS_LAUNCH(T, V, 4); else if (gt == 2) AS_LAUNCH(T, V, 2); else AS_LAUNCH(T, V, 1);             \
@@ -354,5 +374,39 @@ MV_API int mv_attention_sink(const void* q, const void* pool, long long page_str
     }
 #undef AS_PICK
 #undef AS_LAUNCH
+    return mv_launch_status();
+}
+
+// ------------------------------------------------------------------ softmax weights mixed between the heads
+// out[n][h][:] = sum_g talk[h][g] * o_all[n][g][kv head of h][:]: what  sum_j (sum_g talk[h][g] w_g(i, j)) v_(kv(h))(j)
+// is once every head's weights have been applied to every kv head's values.  32-bit sums; out in the model's dtype.
+template <typename T>
+__global__ void __launch_bounds__(256)
+mix_heads_kernel(const float* __restrict__ o_all, const float* __restrict__ talk, T* __restrict__ out, long long total,
+                 int nh, int nkv, int dv) {
+    mv_pdl_begin();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int d = (int)(idx % dv);
+    const long long nhh = idx / dv;
+    const int h = (int)(nhh % nh);
+    const long long n = nhh / nh;
+    const int m = h / (nh / nkv);
+    const float* src = o_all + ((size_t)n * nh * nkv + m) * dv + d;
+    float acc = 0.f;
+    for (int g = 0; g < nh; ++g) acc = fmaf(talk[(size_t)h * nh + g], src[(size_t)g * nkv * dv], acc);
+    out[idx] = mv_from_f32<T>(acc);
+}
+
+MV_API int mv_mix_heads(const float* o_all, const float* talk, void* out, int dtype, int N, int nh, int nkv, int dv,
+                        cudaStream_t stream) {
+    const long long total = (long long)N * nh * dv;
+    if (total <= 0) return 0;
+    if (nkv < 1 || nh % nkv) return (int)cudaErrorInvalidValue;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == MV_DT_BF16)
+        mv_launch(mix_heads_kernel<__nv_bfloat16>, blocks, 256, 0, stream, o_all, talk, (__nv_bfloat16*)out, total, nh, nkv, dv);
+    else
+        mv_launch(mix_heads_kernel<float>, blocks, 256, 0, stream, o_all, talk, (float*)out, total, nh, nkv, dv);
     return mv_launch_status();
 }

@@ -8,7 +8,12 @@
 // blocks of its window; the scores are scaled and capped in float32 before the maximum is taken; the sink
 // starts every row's maximum and denominator; the output is multiplied by the sigmoid of the row's gate;
 // with a chunked mask the walk starts at the first query's chunk and keys before a row's own chunk are masked.
-// Key and value sizes are run-time multiples of 16 up to the template's bounds.
+// Key and value sizes are run-time multiples of 16 up to the template's bounds.  Further parameters, as in
+// attention_sink.cu: a distance bias r1_h ln(1 + r2_h (i - j)) taken off the scores; values that are the keys' first dv
+// elements; a gate per element instead of per head; every head's weights applied to every kv head's values (32-bit
+// results, for weights that are mixed between the heads afterwards).  SPLIT: a softmax weight enters the value
+// product as two bfloat16 numbers, the rounded weight and the rounding's remainder (two mma a tile), which
+// carries 16 bits of its mantissa.
 #include "common.cuh"
 
 namespace {
@@ -37,20 +42,25 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const unsigned*>(&v);
 }
+// the remainders of two values after their rounding to the bfloat16 pair `rounded`, as a bfloat16 pair
+__device__ __forceinline__ unsigned pack_rest(float lo, float hi, unsigned rounded) {
+    return pack_bf16(lo - __uint_as_float(rounded << 16), hi - __uint_as_float(rounded & 0xffff0000u));
+}
 __device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
 
-template <int DKM, int DVM>
+template <int DKM, int DVM, bool SPLIT>
 __global__ void __launch_bounds__(NWARPS * 32)
 attention_sink_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool,
                               long long page_stride, const int* __restrict__ page_table, int table_stride,
                               int page_shift, const int* __restrict__ cu, const int* __restrict__ starts,
                               const float* __restrict__ sinks, const float* __restrict__ gate, int ld_gate,
                               __nv_bfloat16* __restrict__ o, int B, int nh, int nkv, int dk, int dv, float scale,
-                              float cap, int window, int keep_first, int chunk) {
+                              float cap, int window, int keep_first, int chunk, const float* __restrict__ r1,
+                              const float* __restrict__ r2, int v_in_k, int gate_wide, float* __restrict__ o_all) {
     const int ldk = dk + 8, ldv = dv + 8;             // padded rows: conflict-free fragment loads
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [2][KB][ldk]
@@ -63,7 +73,10 @@ attention_sink_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bf
         tile -= tiles;
     }
     if (b >= B) return;
-    const int h = blockIdx.y, g = h / (nh / nkv);
+    // with o_all the grid's y counts (head, kv head whose values are read)
+    const int h = o_all ? blockIdx.y / nkv : blockIdx.y, g = h / (nh / nkv);
+    const int vg = o_all ? blockIdx.y - h * nkv : g;
+    const float db1 = r1 ? r1[h] : 0.f, db2 = r1 ? r2[h] : 0.f;
     const int row0 = cu[b] + tile * QT;
     const int rows_in_seq = cu[b + 1] - cu[b];
     const int nq = min(QT, rows_in_seq - tile * QT);
@@ -72,7 +85,8 @@ attention_sink_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bf
     const int gq = lane >> 2, t4 = lane & 3;
     const int page_size = 1 << page_shift;
     const int* table = page_table + (size_t)b * table_stride;
-    const size_t v_base = (size_t)nkv * page_size * dk;
+    const size_t v_base = v_in_k ? 0 : (size_t)nkv * page_size * dk;
+    const int v_ld = v_in_k ? dk : dv;
 
     const int qi0 = warp * 16 + gq, qi1 = qi0 + 8;
     const int p0 = pos0 + qi0, p1 = pos0 + qi1;
@@ -124,7 +138,8 @@ attention_sink_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bf
             if (c < kchunks)
                 cp_async16(ks + ((size_t)buf * KB + r) * ldk + c * 8, pbase + prow * dk + c * 8);
             else
-                cp_async16(vs + ((size_t)buf * KB + r) * ldv + (c - kchunks) * 8, pbase + v_base + prow * dv + (c - kchunks) * 8);
+                cp_async16(vs + ((size_t)buf * KB + r) * ldv + (c - kchunks) * 8,
+                           pbase + v_base + ((size_t)vg * page_size + (t & (page_size - 1))) * v_ld + (c - kchunks) * 8);
         }
     };
     auto block_of = [&](int it) { return it < n_kept ? it : kb_begin + (it - n_kept); };
@@ -157,7 +172,7 @@ attention_sink_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bf
         }
         // scale and cap, mask, then the running maximum of the two rows
         const int key0 = kb * KB;
-        const bool need_mask = it < n_kept || key0 + KB - 1 > pos0 + warp * 16 ||
+        const bool need_mask = r1 != nullptr || it < n_kept || key0 + KB - 1 > pos0 + warp * 16 ||
                                (chunk > 0 ? key0 < cs1 : (window > 0 && key0 <= pos0 + warp * 16 + 15 - window));
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -176,6 +191,7 @@ attention_sink_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bf
                     const int p = (e < 2) ? p0 : p1;
                     if (t > p || (chunk > 0 ? t < ((e < 2) ? cs0 : cs1)
                                             : (window > 0 && t <= p - window && t >= keep_first))) sc = -INFINITY;
+                    else if (r1) sc -= db1 * __logf(1.0f + db2 * (float)(p - t));
                 }
                 s[j][e] = sc;
             }
@@ -216,6 +232,13 @@ attention_sink_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bf
             const unsigned a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
             const unsigned a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
             const unsigned a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            unsigned c0r = 0, c1r = 0, c2r = 0, c3r = 0;                   // what the rounding left of each weight
+            if (SPLIT) {
+                c0r = pack_rest(s[2 * kk][0], s[2 * kk][1], a0);
+                c1r = pack_rest(s[2 * kk][2], s[2 * kk][3], a1);
+                c2r = pack_rest(s[2 * kk + 1][0], s[2 * kk + 1][1], a2);
+                c3r = pack_rest(s[2 * kk + 1][2], s[2 * kk + 1][3], a3);
+            }
 #pragma unroll
             for (int dj = 0; dj < DVM / 16; ++dj) {
                 if (dj * 16 < dv) {
@@ -224,6 +247,10 @@ attention_sink_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bf
                     ldmatrix_x4_trans(vb, vt + (size_t)(kk * 16 + (mi & 1) * 8 + r) * ldv + dj * 16 + (mi >> 1) * 8);
                     mma_bf16(oacc[2 * dj], a0, a1, a2, a3, vb[0], vb[1]);
                     mma_bf16(oacc[2 * dj + 1], a0, a1, a2, a3, vb[2], vb[3]);
+                    if (SPLIT) {
+                        mma_bf16(oacc[2 * dj], c0r, c1r, c2r, c3r, vb[0], vb[1]);
+                        mma_bf16(oacc[2 * dj + 1], c0r, c1r, c2r, c3r, vb[2], vb[3]);
+                    }
                 }
             }
         }
@@ -234,39 +261,49 @@ attention_sink_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bf
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    float i0 = 1.f / l0, i1 = 1.f / l1;
-    if (qi0 < nq) {
-        if (gate) i0 *= 1.0f / (1.0f + expf(-gate[(size_t)(row0 + qi0) * ld_gate + h]));
-        __nv_bfloat16* dst = o + ((size_t)(row0 + qi0) * nh + h) * dv + 2 * t4;
+    const float i0 = 1.f / l0, i1 = 1.f / l1;
+    auto finish = [&](int qi, float inv, int e0) {
+        if (qi >= nq) return;
+        const size_t row = (size_t)(row0 + qi);
+        const float* grow = gate ? gate + row * ld_gate + (gate_wide ? (size_t)h * dv : (size_t)h) : nullptr;
+        if (grow && !gate_wide) inv *= 1.0f / (1.0f + expf(-grow[0]));
 #pragma unroll
-        for (int j = 0; j < DVM / 8; ++j)
-            if (j * 8 < dv) *reinterpret_cast<unsigned*>(dst + j * 8) = pack_bf16(oacc[j][0] * i0, oacc[j][1] * i0);
-    }
-    if (qi1 < nq) {
-        if (gate) i1 *= 1.0f / (1.0f + expf(-gate[(size_t)(row0 + qi1) * ld_gate + h]));
-        __nv_bfloat16* dst = o + ((size_t)(row0 + qi1) * nh + h) * dv + 2 * t4;
-#pragma unroll
-        for (int j = 0; j < DVM / 8; ++j)
-            if (j * 8 < dv) *reinterpret_cast<unsigned*>(dst + j * 8) = pack_bf16(oacc[j][2] * i1, oacc[j][3] * i1);
-    }
+        for (int j = 0; j < DVM / 8; ++j) {
+            if (j * 8 < dv) {
+                const int d = j * 8 + 2 * t4;
+                float x = oacc[j][e0] * inv, y = oacc[j][e0 + 1] * inv;
+                if (grow && gate_wide) {
+                    x *= 1.0f / (1.0f + expf(-grow[d]));
+                    y *= 1.0f / (1.0f + expf(-grow[d + 1]));
+                }
+                if (o_all)
+                    *reinterpret_cast<float2*>(o_all + ((row * nh + h) * nkv + vg) * dv + d) = make_float2(x, y);
+                else
+                    *reinterpret_cast<unsigned*>(o + (row * nh + h) * dv + d) = pack_bf16(x, y);
+            }
+        }
+    };
+    finish(qi0, i0, 0);
+    finish(qi1, i1, 2);
 }
 
-template <int DKM, int DVM>
+template <int DKM, int DVM, bool SPLIT>
 int launch(const void* q, const void* pool, long long page_stride, const int* page_table, int table_stride,
            int page_shift, const int* cu, const int* starts, const float* sinks, const float* gate, int ld_gate, void* o,
            int N, int B, int nh, int nkv, int dk, int dv, float scale, float cap, int window, int keep_first,
-           int chunk, cudaStream_t stream) {
+           int chunk, const float* r1, const float* r2, int v_in_k, int gate_wide, float* o_all, cudaStream_t stream) {
     const size_t smem = (size_t)2 * KB * (dk + 8 + dv + 8) * sizeof(__nv_bfloat16);
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(attention_sink_prefill_kernel<DKM, DVM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(attention_sink_prefill_kernel<DKM, DVM, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)((size_t)2 * KB * (DKM + 8 + DVM + 8) * sizeof(__nv_bfloat16)));
         attr_set = true;
     }
-    dim3 grid((N + QT - 1) / QT + B, nh);         // an upper bound of the tiles; spare blocks return at once
-    attention_sink_prefill_kernel<DKM, DVM><<<grid, NWARPS * 32, smem, stream>>>(
+    dim3 grid((N + QT - 1) / QT + B, o_all ? nh * nkv : nh);         // an upper bound of the tiles; spare blocks return at once
+    attention_sink_prefill_kernel<DKM, DVM, SPLIT><<<grid, NWARPS * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, page_stride, page_table, table_stride, page_shift, cu,
-        starts, sinks, gate, ld_gate, (__nv_bfloat16*)o, B, nh, nkv, dk, dv, scale, cap, window, keep_first, chunk);
+        starts, sinks, gate, ld_gate, (__nv_bfloat16*)o, B, nh, nkv, dk, dv, scale, cap, window, keep_first, chunk, r1, r2,
+        v_in_k, gate_wide, o_all);
     return mv_launch_status();
 }
 
@@ -280,16 +317,24 @@ MV_API int mv_attention_sink_prefill(const void* q, const void* pool, long long 
                                      int table_stride, int page_size, const int* cu, const int* starts,
                                      const float* sinks, const float* gate, int ld_gate, void* o, int N, int B, int nh,
                                      int nkv, int dk, int dv, float scale, float cap, int window, int keep_first,
-                                     int chunk, cudaStream_t stream) {
+                                     int chunk, const float* r1, const float* r2, int v_in_k, int gate_wide, float* o_all,
+                                     int split, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (nkv < 1 || nh % nkv || (page_size & (page_size - 1)) || dk % 16 || dv % 16 || dk < 16 || dv < 16 || dk > 128 ||
-        dv > 128)
+        dv > 128 || (v_in_k && dv > dk) || (r1 && !r2))
         return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
 #define AS_GO(A, C)                                                                                                  \
-    return launch<A, C>(q, pool, page_stride, page_table, table_stride, page_shift, cu, starts, sinks, gate, ld_gate, o, \
-                        N, B, nh, nkv, dk, dv, scale, cap, window, keep_first, chunk, stream)
+    do {                                                                                                             \
+        if (split)                                                                                                   \
+            return launch<A, C, true>(q, pool, page_stride, page_table, table_stride, page_shift, cu, starts, sinks, gate, \
+                                      ld_gate, o, N, B, nh, nkv, dk, dv, scale, cap, window, keep_first, chunk, r1, r2, \
+                                      v_in_k, gate_wide, o_all, stream);                                             \
+        return launch<A, C, false>(q, pool, page_stride, page_table, table_stride, page_shift, cu, starts, sinks, gate, \
+                                   ld_gate, o, N, B, nh, nkv, dk, dv, scale, cap, window, keep_first, chunk, r1, r2,    \
+                                   v_in_k, gate_wide, o_all, stream);                                                \
+    } while (0)
     if (dk <= 64 && dv <= 64) AS_GO(64, 64);
     if (dk <= 64) AS_GO(64, 128);
     if (dv <= 64) AS_GO(128, 64);

@@ -6,7 +6,8 @@
 //     o_t = S^T q_t                            (the read-out sees the token's own write)
 //
 // with q and k made unit vectors per head first (x / sqrt(sum x^2 + norm_eps), q also times q_scale),
-// beta_t = sigmoid(b_t) per head, and g = exp(-exp(A_log_h) softplus(a + dt_bias)) per head and key channel.
+// beta_t = sigmoid(b_t) per head, and g = exp(-exp(A_log_h) softplus(a + dt_bias)) per head and key channel
+// (with head_decay: a and dt_bias hold one number a head, and all key channels of a head share its decay).
 // Head h reads q and k of head h / (heads / kv_heads).  The state lives in 32-bit floats per sequence slot and
 // is carried from step to step; a step brings any number of next tokens for each of its sequences.  Everything
 // here is 32-bit.
@@ -31,7 +32,7 @@ delta_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict_
                   const float* __restrict__ a, int lda, const float* __restrict__ dt_bias,
                   const float* __restrict__ a_log, float q_scale, float norm_eps, float* __restrict__ state,
                   const int* __restrict__ slots, const int* __restrict__ cu, float* __restrict__ o, int n_heads,
-                  int kv_heads, int dk, int dv) {
+                  int kv_heads, int dk, int dv, int head_decay) {
     mv_pdl_begin();
     extern __shared__ float smem[];
     float* qs = smem;                           // [DR_CHUNK][dk]
@@ -63,7 +64,9 @@ delta_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict_
             const size_t row = (size_t)(row0 + c0 + t);
             qs[idx] = q[row * ldq + (size_t)hk * dk + i];
             ks[idx] = k[row * ldk + (size_t)hk * dk + i];
-            gs[idx] = expf(-rate * dr_softplus(a[row * lda + (size_t)h * dk + i] + dt_bias[(size_t)h * dk + i]));
+            // one decay logit a head (head_decay) or one a head and key channel
+            const size_t ai = head_decay ? (size_t)h : (size_t)h * dk + i;
+            gs[idx] = expf(-rate * dr_softplus(a[row * lda + ai] + dt_bias[ai]));
         }
         for (int idx = tid; idx < nt * DR_COLS; idx += DR_COLS * DR_PART) {
             const int t = idx / DR_COLS, c = idx - t * DR_COLS, col = tile * DR_COLS + c;
@@ -140,14 +143,14 @@ MV_GUARD_SETTER(delta_rule)
 MV_API int mv_delta_scan(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* b, int ldb,
                          const float* a, int lda, const float* dt_bias, const float* a_log, float q_scale, float norm_eps,
                          float* state, const int* slots, const int* cu, float* o, int n_seqs, int n_heads, int kv_heads,
-                         int dk, int dv, cudaStream_t stream) {
+                         int dk, int dv, int head_decay, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (dk < 1 || dk > 256 || dv < 1 || kv_heads < 1 || n_heads % kv_heads) return (int)cudaErrorInvalidValue;
     const dim3 grid((dv + DR_COLS - 1) / DR_COLS, n_heads, n_seqs);
     const size_t smem = (size_t)DR_CHUNK * (3 * dk + DR_COLS + 3) * sizeof(float);
 #define DR_LAUNCH(R)                                                                                                   \
     mv_launch(delta_scan_kernel<R>, grid, DR_COLS * DR_PART, smem, stream, q, ldq, k, ldk, v, ldv, b, ldb, a, lda, dt_bias, \
-              a_log, q_scale, norm_eps, state, slots, cu, o, n_heads, kv_heads, dk, dv)
+              a_log, q_scale, norm_eps, state, slots, cu, o, n_heads, kv_heads, dk, dv, head_decay)
     if (dk <= 32) DR_LAUNCH(4);
     else if (dk <= 64) DR_LAUNCH(8);
     else if (dk <= 128) DR_LAUNCH(16);
@@ -170,7 +173,7 @@ __global__ void __launch_bounds__(256)
 delta_prepare_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
                      const float* __restrict__ b, int ldb, const float* __restrict__ a, int lda,
                      const float* __restrict__ dt_bias, const float* __restrict__ a_log, float q_scale, float norm_eps,
-                     float* __restrict__ prep, int ldp, int n_heads, int kv_heads, int dk) {
+                     float* __restrict__ prep, int ldp, int n_heads, int kv_heads, int dk, int head_decay) {
     mv_pdl_begin();
     const int n = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -198,7 +201,8 @@ delta_prepare_kernel(const float* __restrict__ q, int ldq, const float* __restri
     }
     for (int e = threadIdx.x; e < hk; e += blockDim.x) {
         const int h = e / dk;
-        row[2 * qk + e] = expf(-expf(a_log[h]) * dr_softplus(a[(size_t)n * lda + e] + dt_bias[e]));
+        const int ai = head_decay ? h : e;
+        row[2 * qk + e] = expf(-expf(a_log[h]) * dr_softplus(a[(size_t)n * lda + ai] + dt_bias[ai]));
     }
     for (int h = threadIdx.x; h < n_heads; h += blockDim.x)
         row[2 * qk + hk + h] = 1.0f / (1.0f + expf(-b[(size_t)n * ldb + h]));
@@ -474,12 +478,12 @@ static inline int mv_delta_prep_width(int n_heads, int kv_heads, int dk) {
 MV_API int mv_delta_scan_long(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* b,
                               int ldb, const float* a, int lda, const float* dt_bias, const float* a_log, float q_scale,
                               float norm_eps, float* prep, float* state, const int* slots, const int* cu, float* o, int N,
-                              int n_seqs, int n_heads, int kv_heads, int dk, int dv, cudaStream_t stream) {
+                              int n_seqs, int n_heads, int kv_heads, int dk, int dv, int head_decay, cudaStream_t stream) {
     if (n_seqs <= 0 || N <= 0) return 0;
     if (dk < 1 || dk > 256 || dv < 1 || kv_heads < 1 || n_heads % kv_heads) return (int)cudaErrorInvalidValue;
     const int ldp = mv_delta_prep_width(n_heads, kv_heads, dk);
     mv_launch(delta_prepare_kernel, N, 256, 0, stream, q, ldq, k, ldk, b, ldb, a, lda, dt_bias, a_log, q_scale, norm_eps, prep,
-              ldp, n_heads, kv_heads, dk);
+              ldp, n_heads, kv_heads, dk, head_decay);
     // The walk is launched as an ordinary successor, not a programmatic one.  Started while the preparing kernel's blocks
     // still hold the multiprocessors, its few blocks (one sequence of 16 heads x 128 values: 128) went where room came
     // up first, several to a multiprocessor, and the walk, bound by what ONE multiprocessor issues, took 1.75 times as

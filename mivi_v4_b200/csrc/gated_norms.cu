@@ -244,6 +244,42 @@ MV_API int mv_rmsnorm_add_sum(const float* y1, float s1, const float* y2, float 
     return mv_launch_status();
 }
 
+// ------------------------- a sublayer's result times a vector, added to the stream; then the next norm
+// resid[n, :] += vec * (s1 y1 + s2 y2) (y2 null: s1 y1): a layer whose sublayers' results are multiplied element by
+// element by a learned vector (and a constant, folded into it) before they join the stream.  With w the row it
+// has just completed is normed for the next sublayer: out[n, :] = resid / sqrt(mean(resid^2) + eps) * w.  A thread
+// reads back only elements that it wrote itself.
+template <typename TO>
+__global__ void scaled_add_norm_kernel(const float* __restrict__ y1, float s1, const float* __restrict__ y2, float s2,
+                                       const float* __restrict__ vec, float* __restrict__ resid,
+                                       const float* __restrict__ w, float eps, TO* __restrict__ out, int H) {
+    mv_pdl_begin();
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float v = y2 ? fmaf(s2, y2[base + h], s1 * y1[base + h]) : s1 * y1[base + h];
+        const float r = fmaf(vec[h], v, resid[base + h]);
+        resid[base + h] = r;
+        ss = fmaf(r, r, ss);
+    }
+    if (!w) return;
+    const float scale = 1.0f / sqrtf(mv_block_sum(ss, scratch) / (float)H + eps);
+    for (int h = threadIdx.x; h < H; h += blockDim.x) out[base + h] = mv_from_f32<TO>(resid[base + h] * scale * w[h]);
+}
+
+MV_API int mv_scaled_add_norm(const float* y1, float s1, const float* y2, float s2, const float* vec, float* resid,
+                              const float* w, float eps, void* out, int out_dtype, int N, int H, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if (out_dtype == MV_DT_BF16)
+        mv_launch(scaled_add_norm_kernel<__nv_bfloat16>, N, threads, 0, stream, y1, s1, y2, s2, vec, resid, w, eps,
+                  (__nv_bfloat16*)out, H);
+    else
+        mv_launch(scaled_add_norm_kernel<float>, N, threads, 0, stream, y1, s1, y2, s2, vec, resid, w, eps, (float*)out, H);
+    return mv_launch_status();
+}
+
 // ------------------------- the same, followed by the layer norm of the row it has just completed
 // resid[n, :] += y / rms(y) * w, then out[n, :] = layer_norm(resid[n, :]) * ln_w: the last kernel of a layer and the
 // first of the next in one, for layers that end with a normed input added to the residual stream.  A thread reads

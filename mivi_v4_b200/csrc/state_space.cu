@@ -10,7 +10,8 @@
 
 #define SP_MAX_TAPS 16
 
-// conv state [slot][taps - 1][C], oldest first.  One thread a (token, channel).
+// conv state [slot][taps - 1][C], oldest first.  One thread a (token, channel).  ACT: silu on the result (else none).
+template <bool ACT>
 __global__ void __launch_bounds__(256)
 causal_conv_silu_kernel(const float* __restrict__ u, int ld, const float* __restrict__ taps,
                         const float* __restrict__ bias, const float* __restrict__ state,
@@ -29,10 +30,11 @@ causal_conv_silu_kernel(const float* __restrict__ u, int ld, const float* __rest
         const float x = li >= back ? u[(size_t)(n - back) * ld + c] : st[(size_t)(li + j) * C + c];
         acc = fmaf(taps[(size_t)c * K + j], x, acc);
     }
-    out[idx] = acc / (1.0f + expf(-acc));
+    out[idx] = ACT ? acc / (1.0f + expf(-acc)) : acc;
 }
 
 // The same with four consecutive channels a thread (16-byte loads): C, ld and the pointers allow it.
+template <bool ACT>
 __global__ void __launch_bounds__(256)
 causal_conv_silu_vec_kernel(const float* __restrict__ u, int ld, const float* __restrict__ taps,
                             const float* __restrict__ bias, const float* __restrict__ state,
@@ -71,8 +73,10 @@ causal_conv_silu_vec_kernel(const float* __restrict__ u, int ld, const float* __
             acc.z = fmaf(tp[2 * K + j], x.z, acc.z); acc.w = fmaf(tp[3 * K + j], x.w, acc.w);
         }
     }
-    acc.x = acc.x / (1.0f + expf(-acc.x)); acc.y = acc.y / (1.0f + expf(-acc.y));
-    acc.z = acc.z / (1.0f + expf(-acc.z)); acc.w = acc.w / (1.0f + expf(-acc.w));
+    if (ACT) {
+        acc.x = acc.x / (1.0f + expf(-acc.x)); acc.y = acc.y / (1.0f + expf(-acc.y));
+        acc.z = acc.z / (1.0f + expf(-acc.z)); acc.w = acc.w / (1.0f + expf(-acc.w));
+    }
     *reinterpret_cast<float4*>(out + (size_t)n * C + c) = acc;
 }
 
@@ -160,25 +164,38 @@ MV_API int mv_ssm_decode_prepare(const float* u, int ld, const float* taps, cons
 }
 
 // u: the convolution's input columns [N, C] with row stride ld; taps [C, K]; bias [C] or null; state
-// [slots][K - 1][C]; out [N, C] dense.  Two kernels: the outputs (which read the kept inputs), then the kept
-// inputs' update.
-MV_API int mv_causal_conv_silu(const float* u, int ld, const float* taps, const float* bias, float* state,
-                               const int* seq_of, const int* cu, const int* slots, float* out, int N, int n_seqs,
-                               int C, int K, cudaStream_t stream) {
+// [slots][K - 1][C]; out [N, C] dense; act: 1 silu on the result, 0 none.  Two kernels: the outputs (which read
+// the kept inputs), then the kept inputs' update.
+MV_API int mv_causal_conv(const float* u, int ld, const float* taps, const float* bias, float* state,
+                          const int* seq_of, const int* cu, const int* slots, float* out, int N, int n_seqs,
+                          int C, int K, int act, cudaStream_t stream) {
     if (N <= 0 || n_seqs <= 0) return 0;
     if (K < 1 || K > SP_MAX_TAPS || C < 1) return (int)cudaErrorInvalidValue;
     const long long total = (long long)N * C;
     const bool wide = C % 4 == 0 && ld % 4 == 0 && N >= 64 &&
                       (((uintptr_t)u | (uintptr_t)bias | (uintptr_t)state | (uintptr_t)out | (uintptr_t)taps) & 15) == 0;
-    if (wide)
-        mv_launch(causal_conv_silu_vec_kernel, (unsigned)((total / 4 + 255) / 256), 256, 0, stream, u, ld, taps, bias,
-                  (const float*)state, seq_of, cu, slots, out, total / 4, C, K);
-    else
-        mv_launch(causal_conv_silu_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, u, ld, taps, bias,
-                  (const float*)state, seq_of, cu, slots, out, total, C, K);
+#define SP_CONV(KERNEL, COUNT)                                                                                      \
+    do {                                                                                                            \
+        if (act)                                                                                                    \
+            mv_launch(KERNEL<true>, (unsigned)(((COUNT) + 255) / 256), 256, 0, stream, u, ld, taps, bias,           \
+                      (const float*)state, seq_of, cu, slots, out, (COUNT), C, K);                                  \
+        else                                                                                                        \
+            mv_launch(KERNEL<false>, (unsigned)(((COUNT) + 255) / 256), 256, 0, stream, u, ld, taps, bias,          \
+                      (const float*)state, seq_of, cu, slots, out, (COUNT), C, K);                                  \
+    } while (0)
+    if (wide) SP_CONV(causal_conv_silu_vec_kernel, total / 4);
+    else SP_CONV(causal_conv_silu_kernel, total);
+#undef SP_CONV
     if (K > 1)
         mv_launch(causal_conv_state_kernel, dim3((C + 255) / 256, n_seqs), 256, 0, stream, u, ld, state, cu, slots, C, K);
     return mv_launch_status();
+}
+
+// The same with silu, under the name it had first.
+MV_API int mv_causal_conv_silu(const float* u, int ld, const float* taps, const float* bias, float* state,
+                               const int* seq_of, const int* cu, const int* slots, float* out, int N, int n_seqs,
+                               int C, int K, cudaStream_t stream) {
+    return mv_causal_conv(u, ld, taps, bias, state, seq_of, cu, slots, out, N, n_seqs, C, K, 1, stream);
 }
 
 // raw [N, H] with row stride ld; dt_bias, a_log [H]; log_a, b_out [N, H] dense.

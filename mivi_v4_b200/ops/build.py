@@ -28,7 +28,7 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["elementwise.cu", "gemm_simt.cu", "shortconv.cu", "attention.cu", "attention_decode.cu",
              "sampling.cu", "gated_norms.cu", "decay_scan.cu", "attention_sink.cu", "scalar_scan.cu", "state_space.cu",
-             "routed_experts.cu", "latent_attention.cu", "delta_rule.cu"],
+             "routed_experts.cu", "latent_attention.cu", "delta_rule.cu", "gated_recurrence.cu"],
     "bf16": ["gemm_small_m.cu", "gemm_tc.cu", "gemm_tc_pair.cu", "gemm_tc_swap.cu", "attention_prefill.cu",
              "attention_prefill_tc.cu", "attention_decode_tc.cu", "attention_sink_prefill.cu",
              "latent_attention_prefill.cu"],

@@ -60,7 +60,11 @@ _SIGNATURES = {
         "mv_qkv_prepare_wide": [_P, _I, _P, _P, _F, _I, _P, _P, _P, _P, _I, _I, _P, _Q, _P, _I, _I, _I, _I, _I, _I, _I,
                                 _F, _P],
         "mv_attention_sink": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I,
-                              _I, _I, _P],
+                              _I, _I, _P, _P, _I, _I, _P, _P],
+        "mv_mix_heads": [_P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "mv_block_gates": [_P, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P],
+        "mv_gated_recurrence": [_P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "mv_scaled_add_norm": [_P, _F, _P, _F, _P, _P, _P, _F, _P, _I, _I, _I, _P],
         "mv_embed_scaled_pos": [_P, _I, _P, _F, _P, _P, _P, _P, _I, _I, _I, _P],
         "mv_softcap": [_P, _Q, _F, _P],
         "mv_rmsnorm_add_sum": [_P, _F, _P, _F, _P, _P, _P, _I, _I, _I, _F, _P],
@@ -70,7 +74,7 @@ _SIGNATURES = {
         "mv_scalar_scan_chunked": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _I,
                                    _I, _I, _I, _I, _I, _P],
         "mv_memory_gates": [_P, _I, _P, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _P],
-        "mv_causal_conv_silu": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "mv_causal_conv": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "mv_ssm_decode_prepare": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P],
         "mv_step_size": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
         "mv_route": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
@@ -82,8 +86,8 @@ _SIGNATURES = {
         "mv_latent_prepare": [_P, _I, _I, _I, _P, _F, _P, _P, _P, _P, _I, _I, _P, _Q, _I, _P, _I, _I, _I, _I, _I, _I, _P],
         "mv_head_product": [_P, _Q, _I, _P, _I, _I, _P, _Q, _P, _I, _Q, _I, _I, _I, _I, _I, _P],
         "mv_latent_attention": [_P, _P, _Q, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
-        "mv_delta_scan_long": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _F, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-        "mv_delta_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _F, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "mv_delta_scan_long": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _F, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        "mv_delta_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _F, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
         "mv_expert_rank": [_P, _I, _I, _P, _P, _P],
         "mv_expert_gather": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
         "mv_expert_tiles": [_P, _I, _I, _P, _P, _I, _P],
@@ -106,7 +110,7 @@ _SIGNATURES = {
                                   _P, _I, _I, _I, _F, _P, _Q, _P, _P],
         "mv_attention_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
         "mv_attention_sink_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I,
-                                      _I, _I, _P],
+                                      _I, _I, _P, _P, _I, _I, _P, _I, _P],
         "mv_attention_decode_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
         "mv_attention_prefill_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P, _P],
         "mv_latent_query": [_P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P],
@@ -317,7 +321,7 @@ def _need(t: Optional[torch.Tensor], name: str, dtype=None, shape=None, optional
 
 _launches = 0
 # kernels launched by one call of each entry point
-_KERNELS_PER_CALL = {"mv_shortconv": 2, "mv_decay_scan_chunked": 2, "mv_causal_conv_silu": 2, "mv_scalar_scan_chunked": 2}
+_KERNELS_PER_CALL = {"mv_shortconv": 2, "mv_decay_scan_chunked": 2, "mv_causal_conv": 2, "mv_scalar_scan_chunked": 2}
 
 
 def launch_count() -> int:
@@ -545,6 +549,63 @@ def rmsnorm_add_sum(y1: torch.Tensor, w: torch.Tensor, eps: float, resid: torch.
     return resid
 
 
+def scaled_add_norm(y1: torch.Tensor, vec: torch.Tensor, resid: torch.Tensor, *, s1: float = 1.0,
+                    y2: Optional[torch.Tensor] = None, s2: float = 1.0, w: Optional[torch.Tensor] = None,
+                    eps: float = 0.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """resid[n, :] += vec * (s1 y1[n, :] + s2 y2[n, :]) (``y2`` None: s1 y1): a sublayer's result, or the weighted
+    sum of two, times a learned vector, joins the float32 stream.  With ``w`` and ``out`` the completed row is
+    normed for the next sublayer in the same kernel: out[n, :] = resid / sqrt(mean(resid^2) + eps) * w."""
+    N, H = resid.shape
+    if (w is None) != (out is None):
+        raise KernelError("scaled_add_norm: the norm's weight and its output come together")
+    _check(_fn("core", "mv_scaled_add_norm")(
+        _need(y1, "scaled_add_norm y1", torch.float32, (N, H)), float(s1),
+        _need(y2, "scaled_add_norm y2", torch.float32, (N, H), True), float(s2),
+        _need(vec, "scaled_add_norm vector", torch.float32, (H,)), _need(resid, "resid", torch.float32),
+        _need(w, "norm weight", torch.float32, (H,), True), float(eps), _need(out, "scaled_add_norm out", None, (N, H), True),
+        _dt(out) if out is not None else F32, N, H, _stream()), "mv_scaled_add_norm")
+    account(N * H * (12 + (4 if y2 is not None else 0) + (out.element_size() if out is not None else 0)))
+    return resid
+
+
+def block_gates(u: torch.Tensor, wa_t: torch.Tensor, wi_t: torch.Tensor, ba: torch.Tensor, bi: torch.Tensor,
+                lam: torch.Tensor, c: float, a_out: torch.Tensor, x_out: torch.Tensor) -> None:
+    """The gates of a gated linear recurrence, float32: with u [N, C] cut into ``n_blocks`` = wa_t.shape[0] equal
+    parts, r = sigmoid(A_b u_b + ba), i = sigmoid(B_b u_b + bi); a_out = exp(-c r softplus(lam)) and
+    x_out = sqrt(1 - a^2) i u.  ``wa_t``, ``wi_t`` [n_blocks, in, out]: the parts' square matrices TRANSPOSED."""
+    N, C = u.shape
+    nb = wa_t.shape[0]
+    if nb < 1 or C % nb:
+        raise KernelError(f"block_gates: {C} channels do not split into {nb} parts")
+    bs = C // nb
+    if bs * 64 > 200 * 1024:
+        raise KernelError(f"block_gates: parts of {bs} channels are more than a block holds (3,200)")
+    _check(_fn("core", "mv_block_gates")(
+        _need(u, "block_gates input", torch.float32, (N, C)), _need(wa_t, "block_gates A", torch.float32, (nb, bs, bs)),
+        _need(wi_t, "block_gates B", torch.float32, (nb, bs, bs)), _need(ba, "block_gates A bias", torch.float32, (C,)),
+        _need(bi, "block_gates B bias", torch.float32, (C,)), _need(lam, "block_gates lambda", torch.float32, (C,)), float(c),
+        _need(a_out, "block_gates decay out", torch.float32, (N, C)), _need(x_out, "block_gates input out", torch.float32, (N, C)),
+        N, C, nb, _stream()), "mv_block_gates")
+    account(N * C * 12 + 2 * nb * bs * bs * 4, 4 * N * C * bs)
+
+
+def gated_recurrence(a: torch.Tensor, x: torch.Tensor, y: torch.Tensor, state: torch.Tensor, slots, cu, out: torch.Tensor,
+                     n_seqs: int, max_len: int = 1) -> torch.Tensor:
+    """S_t = a_t S_(t-1) + x_t per channel along each sequence, from the state kept per slot (float32 [slots, C],
+    brought up to date); out = S * gelu_tanh(y) in ``out``'s dtype.  a, x float32 [N, C]; y float32 [N, C], a column
+    slice is fine.  ``max_len``: the most tokens that a sequence brings; long sequences are walked in pieces."""
+    N, C = out.shape
+    yp, ldy = _cols(y, "gated_recurrence y", N, C)
+    _guard("core", "gated_recurrence", out.device, n_slots=state.shape[0])
+    _check(_fn("core", "mv_gated_recurrence")(
+        _need(a, "gated_recurrence decay", torch.float32, (N, C)), _need(x, "gated_recurrence input", torch.float32, (N, C)),
+        yp, ldy, _need(state, "gated_recurrence state", torch.float32, (None, C)), _need(slots, "slots", torch.int32),
+        _need(cu, "cu", torch.int32), _need(out, "gated_recurrence out"), _dt(out), int(n_seqs), C, int(max_len), _stream()),
+        "mv_gated_recurrence")
+    account(N * C * (12 + out.element_size()) + 2 * n_seqs * C * 4, 4 * N * C)
+    return out
+
+
 def scalar_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_a: torch.Tensor, b: torch.Tensor,
                 state: torch.Tensor, slots: torch.Tensor, cu: torch.Tensor, out: torch.Tensor, n_seqs: int,
                 n_heads: int, dk: int, dv: int, *, heads_per_group: int = 1, skip: Optional[torch.Tensor] = None,
@@ -619,25 +680,32 @@ def memory_gates(zi: torch.Tensor, zf: torch.Tensor, bi: torch.Tensor, bf: torch
     account(N * n_heads * 20)
 
 
-def causal_conv_silu(u: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
-                     seq_of: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, n_seqs: int) -> torch.Tensor:
-    """out = silu(bias + sum_j taps[:, j] * u[t - (K - 1) + j]) per channel along each sequence (the last tap is the
-    current token's; zeros before a sequence's start), float32.  ``u`` [N, C] may be a column slice; ``state``
-    [slots, K - 1, C] holds each sequence's last K - 1 inputs and is brought up to date."""
+def causal_conv(u: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+                seq_of: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, n_seqs: int,
+                act: bool = False) -> torch.Tensor:
+    """out = bias + sum_j taps[:, j] * u[t - (K - 1) + j] per channel along each sequence (the last tap is the
+    current token's; zeros before a sequence's start), float32; with ``act`` silu of that.  ``u`` [N, C] may be a
+    column slice; ``state`` [slots, K - 1, C] holds each sequence's last K - 1 inputs and is brought up to date."""
     N, C = out.shape
     K = taps.shape[1]
     if not 1 <= K <= MAX_CONV_K:
-        raise KernelError(f"causal_conv_silu: {K} taps are outside 1..{MAX_CONV_K}")
-    up, ldu = _cols(u, "causal_conv_silu input", N, C)
+        raise KernelError(f"causal_conv: {K} taps are outside 1..{MAX_CONV_K}")
+    up, ldu = _cols(u, "causal_conv input", N, C)
     if K > 1:
         _guard("core", "state_space", out.device, n_slots=state.shape[0])
-    _check(_fn("core", "mv_causal_conv_silu")(
+    _check(_fn("core", "mv_causal_conv")(
         up, ldu, _need(taps, "conv taps", torch.float32, (C, K)), _need(bias, "conv bias", torch.float32, (C,), True),
         _need(state, "conv state", torch.float32, (None, max(K - 1, 0), C)) if K > 1 else None,
         _need(seq_of, "seq_of", torch.int32), _need(cu, "cu", torch.int32), _need(slots, "slots", torch.int32),
-        _need(out, "causal_conv_silu out", torch.float32), N, int(n_seqs), C, K, _stream()), "mv_causal_conv_silu")
+        _need(out, "causal_conv out", torch.float32), N, int(n_seqs), C, K, int(bool(act)), _stream()), "mv_causal_conv")
     account(N * C * 8 + 2 * n_seqs * (K - 1) * C * 4, 2 * N * C * K)
     return out
+
+
+def causal_conv_silu(u: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+                     seq_of: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, n_seqs: int) -> torch.Tensor:
+    """:func:`causal_conv` followed by silu."""
+    return causal_conv(u, taps, bias, state, seq_of, cu, slots, out, n_seqs, act=True)
 
 
 def step_size(raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, log_a: torch.Tensor, b: torch.Tensor) -> None:
@@ -966,31 +1034,64 @@ def qkv_prepare_wide(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Optiona
 def attention_sink(q: torch.Tensor, pool: torch.Tensor, page_size: int, page_table, positions, seq_of,
                    out: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, scale: float, *, softcap: float = 0.0,
                    window: int = 0, keep_first: int = 0, sinks: Optional[torch.Tensor] = None,
-                   gate: Optional[torch.Tensor] = None, head_tile: int = 0, chunk: int = 0) -> torch.Tensor:
+                   gate: Optional[torch.Tensor] = None, head_tile: int = 0, chunk: int = 0,
+                   distance_bias: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, values_in_keys: bool = False,
+                   gate_wide: bool = False, out_all: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal softmax attention of every token of the step over its sequence's cache (which already holds the
     step's own keys), keys of size dk and values of size dv.  ``softcap`` c > 0: s <- c tanh(s / c).  ``window``
     w > 0 with ``keep_first`` f: query i reads key j if i - j < w or j < f.  ``sinks`` [nh]: exp(sink) joins
     each head's denominator.  ``gate``: float32 logits [N, nh] (a column slice is fine); the head's output is
     multiplied by sigmoid(gate).  ``chunk`` c > 0 (instead of a window): query i reads key j <= i only if
     i // c == j // c.  ``head_tile``: how many query heads of a kv head share a block and its loads
-    (1, 2 or 4; 0: the kernel chooses by the step's size)."""
+    (1, 2 or 4; 0: the kernel chooses by the step's size).  ``distance_bias`` (r1, r2), float32 [nh] each:
+    r1_h ln(1 + r2_h (i - j)) is taken off the score.  ``values_in_keys``: the values are the first dv elements of
+    the key rows and a page holds key rows only.  ``gate_wide``: ``gate`` is [N, nh * dv], one logit an element.
+    ``out_all``: float32 [N, nh, nkv, dv]; every head's weights are applied to the values of every kv head and
+    written there (``out`` is then left alone): what :func:`mix_heads` needs."""
     N = q.shape[0]
     if not (1 <= dk <= MAX_HEAD_DIM and 1 <= dv <= MAX_HEAD_DIM):
         raise KernelError(f"attention_sink: key size {dk} and value size {dv} must lie in 1..{MAX_HEAD_DIM}")
     if nkv < 1 or nh % nkv:
         raise KernelError(f"attention: {nh} heads are not a multiple of {nkv} kv heads")
-    _check_kv_wide(pool, nkv, page_size, dk, dv, "attention_sink")
-    if q.dtype != pool.dtype or out.dtype != q.dtype:
+    _check_kv_wide(pool, nkv, page_size, dk, 0 if values_in_keys else dv, "attention_sink")
+    if q.dtype != pool.dtype or (out_all is None and out.dtype != q.dtype):
         raise KernelError(f"attention: q {q.dtype}, cache {pool.dtype}, out {out.dtype} must agree")
-    gp, ldg = _cols(gate, "attention gate", N, nh) if gate is not None else (None, 0)
+    gp, ldg = _cols(gate, "attention gate", N, nh * dv if gate_wide else nh) if gate is not None else (None, 0)
+    r1, r2 = _bias_pair(distance_bias, nh, values_in_keys, dk, dv)
     _guard("core", "attention_sink", q.device, n_pages=pool.shape[0])
     _check(_fn("core", "mv_attention_sink")(
         _need(q, "q", None, (N, nh * dk)), _need(pool, "cache pool"), pool.stride(0),
         _need(page_table, "page table", torch.int32), page_table.shape[1], page_size,
         _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
-        _need(sinks, "sinks", torch.float32, (nh,), True), gp, ldg, _need(out, "attention out", None, (N, nh * dv)),
+        _need(sinks, "sinks", torch.float32, (nh,), True), gp, ldg,
+        _need(out, "attention out", None, (N, nh * dv), out_all is not None),
         _dt(q), N, nh, nkv, dk, dv, float(scale), float(softcap), int(window), int(keep_first), int(head_tile),
-        int(chunk), _stream()), "mv_attention_sink")
+        int(chunk), r1, r2, int(bool(values_in_keys)), int(bool(gate_wide)),
+        _need(out_all, "attention out of all kv heads", torch.float32, (N, nh, nkv, dv), True), _stream()), "mv_attention_sink")
+    return out if out_all is None else out_all
+
+
+def _bias_pair(distance_bias, nh: int, values_in_keys: bool, dk: int, dv: int):
+    if values_in_keys and dv > dk:
+        raise KernelError(f"attention: values of {dv} cannot be the first elements of keys of {dk}")
+    if distance_bias is None:
+        return None, None
+    r1, r2 = distance_bias
+    return _need(r1, "distance bias r1", torch.float32, (nh,)), _need(r2, "distance bias r2", torch.float32, (nh,))
+
+
+def mix_heads(o_all: torch.Tensor, talk: torch.Tensor, out: torch.Tensor, nh: int, nkv: int, dv: int) -> torch.Tensor:
+    """out[n, h, :] = sum_g talk[h, g] * o_all[n, g, kv head of h, :]: attention whose softmax weights are mixed
+    between the heads after the softmax, w'_h = sum_g talk[h, g] w_g, each head applying its mixed weights to the
+    values of its own kv head; ``o_all`` float32 [N, nh, nkv, dv] holds every head's weights applied to every kv
+    head's values (:func:`attention_sink` with ``out_all``); ``talk`` float32 [nh, nh]; ``out`` [N, nh * dv]."""
+    N = out.shape[0]
+    if nkv < 1 or nh % nkv:
+        raise KernelError(f"mix_heads: {nh} heads are not a multiple of {nkv} kv heads")
+    _check(_fn("core", "mv_mix_heads")(
+        _need(o_all, "mix_heads input", torch.float32, (N, nh, nkv, dv)), _need(talk, "mix_heads talk", torch.float32, (nh, nh)),
+        _need(out, "mix_heads out", None, (N, nh * dv)), _dt(out), N, nh, nkv, dv, _stream()), "mv_mix_heads")
+    account(N * nh * dv * (4 * nkv + out.element_size()), 2 * N * nh * nh * dv)
     return out
 
 
@@ -1005,29 +1106,36 @@ def attention_sink_prefill(q: torch.Tensor, pool: torch.Tensor, page_size: int, 
                            out: torch.Tensor, n_seqs: int, nh: int, nkv: int, dk: int, dv: int, scale: float, *,
                            softcap: float = 0.0, window: int = 0, keep_first: int = 0,
                            sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                           chunk: int = 0) -> torch.Tensor:
+                           chunk: int = 0, distance_bias: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                           values_in_keys: bool = False, gate_wide: bool = False,
+                           out_all: Optional[torch.Tensor] = None, split_weights: bool = False) -> torch.Tensor:
     """:func:`attention_sink` for a step with many query tokens, on the tensor cores (bfloat16, key and value
     sizes 16..128 in steps of 16).  The step's tokens are packed sequence by sequence (``cu``), sequence b
-    starting at position ``starts[b]``."""
+    starting at position ``starts[b]``.  ``split_weights``: a softmax weight enters the value product as two
+    bfloat16 numbers (the rounded weight and what the rounding left), 16 bits of its mantissa instead of 8."""
     N = q.shape[0]
     if not attention_sink_prefill_supported(q.dtype, dk, dv):
         raise KernelError(f"attention_sink_prefill: needs bfloat16 and key and value sizes 16..128 in steps of 16, "
                           f"got {q.dtype}, {dk}, {dv}")
     if nkv < 1 or nh % nkv:
         raise KernelError(f"attention: {nh} heads are not a multiple of {nkv} kv heads")
-    _check_kv_wide(pool, nkv, page_size, dk, dv, "attention_sink_prefill")
-    if q.dtype != pool.dtype or out.dtype != q.dtype:
+    _check_kv_wide(pool, nkv, page_size, dk, 0 if values_in_keys else dv, "attention_sink_prefill")
+    if q.dtype != pool.dtype or (out_all is None and out.dtype != q.dtype):
         raise KernelError(f"attention: q {q.dtype}, cache {pool.dtype}, out {out.dtype} must agree")
-    gp, ldg = _cols(gate, "attention gate", N, nh) if gate is not None else (None, 0)
+    gp, ldg = _cols(gate, "attention gate", N, nh * dv if gate_wide else nh) if gate is not None else (None, 0)
+    r1, r2 = _bias_pair(distance_bias, nh, values_in_keys, dk, dv)
     _guard("bf16", "attention_sink_prefill", q.device, n_pages=pool.shape[0])
     _check(_fn("bf16", "mv_attention_sink_prefill")(
         _need(q, "q", None, (N, nh * dk)), _need(pool, "cache pool"), pool.stride(0),
         _need(page_table, "page table", torch.int32), page_table.shape[1], page_size,
         _need(cu, "cu", torch.int32), _need(starts, "starts", torch.int32),
-        _need(sinks, "sinks", torch.float32, (nh,), True), gp, ldg, _need(out, "attention out", None, (N, nh * dv)),
-        N, n_seqs, nh, nkv, dk, dv, float(scale), float(softcap), int(window), int(keep_first), int(chunk), _stream()),
-        "mv_attention_sink_prefill")
-    return out
+        _need(sinks, "sinks", torch.float32, (nh,), True), gp, ldg,
+        _need(out, "attention out", None, (N, nh * dv), out_all is not None),
+        N, n_seqs, nh, nkv, dk, dv, float(scale), float(softcap), int(window), int(keep_first), int(chunk), r1, r2,
+        int(bool(values_in_keys)), int(bool(gate_wide)),
+        _need(out_all, "attention out of all kv heads", torch.float32, (N, nh, nkv, dv), True), int(bool(split_weights)),
+        _stream()), "mv_attention_sink_prefill")
+    return out if out_all is None else out_all
 
 
 def embed_bigram(table: torch.Tensor, bigram: torch.Tensor, tokens, positions, seq_of, cu, slots, prev: torch.Tensor,
@@ -1236,12 +1344,13 @@ DELTA_LONG_STEP = 8
 def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, a: torch.Tensor,
                dt_bias: torch.Tensor, a_log: torch.Tensor, state: torch.Tensor, slots, cu, out: torch.Tensor,
                n_seqs: int, n_heads: int, kv_heads: int, dk: int, dv: int, *, q_scale: float,
-               norm_eps: float = 1e-6, max_len: int = 1, ws=None) -> torch.Tensor:
+               norm_eps: float = 1e-6, max_len: int = 1, ws=None, head_decay: bool = False) -> torch.Tensor:
     """The gated delta rule with a decay per key channel, token by token: per head S <- diag(g) S;
     u = sigmoid(beta) (v - S^T k); S <- S + k u^T; o = S^T q, with q and k made unit vectors per head first
     (x / sqrt(sum x^2 + norm_eps), q also times ``q_scale``) and g = exp(-exp(a_log_h) softplus(a + dt_bias)).
     q, k [N, kv_heads * dk] (head h reads head h // (n_heads / kv_heads)), v [N, n_heads * dv], beta [N, n_heads],
-    a [N, n_heads * dk]: float32, column slices are fine; ``state`` float32 [slots, n_heads, dv, dk]; ``out``
+    a [N, n_heads * dk] (with ``head_decay`` one decay a head: a [N, n_heads], dt_bias [n_heads]): float32, column
+    slices are fine; ``state`` float32 [slots, n_heads, dv, dk]; ``out``
     float32 [N, n_heads * dv].  ``max_len``: the most tokens that a sequence brings; from ``DELTA_LONG_STEP`` on
     (and with a workspace ``ws`` for the prepared rows) unit vectors, decays and beta are worked out once a token by
     a kernel of their own and the walk along the sequence holds the recurrence alone."""
@@ -1253,27 +1362,28 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Te
     kp, ldk = _cols(k, "delta_scan k", N, kv_heads * dk)
     vp, ldv = _cols(v, "delta_scan v", N, n_heads * dv)
     bp, ldb = _cols(beta, "delta_scan beta", N, n_heads)
-    ap, lda = _cols(a, "delta_scan decay", N, n_heads * dk)
+    n_decays = n_heads if head_decay else n_heads * dk
+    ap, lda = _cols(a, "delta_scan decay", N, n_decays)
     _guard("core", "delta_rule", out.device, n_slots=state.shape[0])
     if long_step:
         # a row: q and k of the q/k heads, the decays, beta, k . q; padded to 16 bytes (as the kernel lays it out)
         width = (2 * kv_heads * dk + n_heads * dk + n_heads + kv_heads + 3) & ~3
         prep = ws.get("delta_scan.prep", (N, width), torch.float32)
         _check(_fn("core", "mv_delta_scan_long")(
-            qp, ldq, kp, ldk, vp, ldv, bp, ldb, ap, lda, _need(dt_bias, "dt_bias", torch.float32, (n_heads * dk,)),
+            qp, ldq, kp, ldk, vp, ldv, bp, ldb, ap, lda, _need(dt_bias, "dt_bias", torch.float32, (n_decays,)),
             _need(a_log, "A_log", torch.float32, (n_heads,)), float(q_scale), float(norm_eps), prep.data_ptr(),
             _need(state, "delta_scan state", torch.float32, (None, n_heads, dv, dk)), _need(slots, "slots", torch.int32),
             _need(cu, "cu", torch.int32), _need(out, "delta_scan out", torch.float32, (N, n_heads * dv)), N, int(n_seqs),
-            n_heads, kv_heads, dk, dv, _stream()), "mv_delta_scan_long")
+            n_heads, kv_heads, dk, dv, int(bool(head_decay)), _stream()), "mv_delta_scan_long")
         account(2 * n_seqs * n_heads * dv * dk * 4 + N * (2 * kv_heads * dk + n_heads * (2 * dv + dk + 1)) * 4
                 + 2 * prep.numel() * 4, 6 * N * n_heads * dk * dv)
         return out
     _check(_fn("core", "mv_delta_scan")(
-        qp, ldq, kp, ldk, vp, ldv, bp, ldb, ap, lda, _need(dt_bias, "dt_bias", torch.float32, (n_heads * dk,)),
+        qp, ldq, kp, ldk, vp, ldv, bp, ldb, ap, lda, _need(dt_bias, "dt_bias", torch.float32, (n_decays,)),
         _need(a_log, "A_log", torch.float32, (n_heads,)), float(q_scale), float(norm_eps),
         _need(state, "delta_scan state", torch.float32, (None, n_heads, dv, dk)), _need(slots, "slots", torch.int32),
         _need(cu, "cu", torch.int32), _need(out, "delta_scan out", torch.float32, (N, n_heads * dv)), int(n_seqs), n_heads,
-        kv_heads, dk, dv, _stream()), "mv_delta_scan")
+        kv_heads, dk, dv, int(bool(head_decay)), _stream()), "mv_delta_scan")
     account(2 * n_seqs * n_heads * dv * dk * 4 + N * (2 * kv_heads * dk + n_heads * (2 * dv + dk + 1)) * 4,
             6 * N * n_heads * dk * dv)
     return out

@@ -148,6 +148,101 @@ class PreNormOptionalBlock(Part):
                     self.token_input.forward(resid, step)
 
 
+@register("block", "prenorm_scaled")
+class PreNormScaledBlock(Part):
+    """x += m * s1 * mixer(norm1(x)); then, if the layer has a feed-forward, x += m * s2 * feed_forward(norm2(x)):
+    every sublayer's result is multiplied element by element by a learned vector of the stream's width (``scale1``,
+    ``scale2``) and by the constant ``residual_mult`` m before it joins the stream.  The norms are root-mean-square
+    norms.  A sublayer writes its result into a float32 buffer of its own (a mixer with ``forward_sum`` gives its two
+    branches apart, with their factors); ONE kernel then adds it, times m * s, to the float32 stream and norms the
+    completed row for the sublayer that reads it next, this block's feed-forward or the next block's mixer."""
+
+    nested_roles = {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "ffn": "feed_forward"}
+
+    def __init__(self, hidden: int, mixer_norm, mixer, ffn_norm=None, ffn=None, residual_mult: float = 1.0):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together or not at all")
+        for norm in (mixer_norm, ffn_norm):
+            if norm is not None and not isinstance(norm, RMSNorm):
+                raise ValueError("the norms of a prenorm_scaled block are rmsnorm parts")
+        for part in (mixer, ffn):
+            if part is not None and not (getattr(part, "overwrites", False) or hasattr(part, "forward_sum")):
+                raise ValueError(f"{getattr(part, 'kind', '?')} cannot write its result apart from the residual stream")
+        self.hidden, self.mult = int(hidden), float(residual_mult)
+        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
+
+    def nested(self):
+        parts = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "ffn_norm": self.ffn_norm, "ffn": self.ffn}
+        return {k: v for k, v in parts.items() if v is not None}
+
+    def param_specs(self):
+        from .spec import ParamSpec
+        specs = {"scale1": ParamSpec((self.hidden,), "vector", "norm")}
+        if self.ffn is not None:
+            specs["scale2"] = ParamSpec((self.hidden,), "vector", "norm")
+        return specs
+
+    def load(self, t) -> None:
+        # m * s as one float32 vector a sublayer
+        self.vec1 = (t["scale1"].float() * self.mult).contiguous()
+        self.vec2 = (t["scale2"].float() * self.mult).contiguous() if self.ffn is not None else None
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def entry_link(self, step):
+        """No product carries this block's norms; the method is there so that the model tells ``forward`` which
+        block runs next (``after``)."""
+        return None
+
+    def _run(self, part, name, u, step, *args):
+        """The sublayer's result in a buffer of its own, as a list of (rows, factor)."""
+        if hasattr(part, "forward_sum"):
+            return part.forward_sum(u, step, *args)
+        y = self.scratch(step, name, (u.shape[0], self.hidden), torch.float32)
+        part.forward(u, y, step, *args, accumulate=False)
+        return [(y, 1.0)]
+
+    def _join(self, branches, vec, resid, norm, out):
+        (y1, s1), rest = branches[0], branches[1:]
+        if len(rest) > 1:
+            raise ValueError("at most two branches are summed in the joining kernel")
+        y2, s2 = rest[0] if rest else (None, 1.0)
+        if norm is None:
+            K.scaled_add_norm(y1, vec, resid, s1=s1, y2=y2, s2=s2)
+        else:
+            K.scaled_add_norm(y1, vec, resid, s1=s1, y2=y2, s2=s2, w=norm.weight, eps=norm.eps, out=out)
+
+    def forward(self, resid, step, view, after=None) -> None:
+        N, H = resid.shape
+        handed, step.handed = getattr(step, "handed", None), None
+        if handed is not None and handed[0] is self.mixer_norm:
+            u = handed[1]
+        else:
+            u = self.scratch(step, "normed", (N, H), step.dtype)
+            with profile_stage("norm"):
+                self.mixer_norm.forward(resid, u)
+        # the block after this one, if it is of this kind, gets its first norm's rows from this block's last kernel
+        nxt = after.mixer_norm if isinstance(after, PreNormScaledBlock) else None
+        # (into the buffer that held this block's own: its mixer is done with them by then)
+        nxt_out = self.scratch(step, "normed", (N, H), step.dtype) if nxt is not None else None
+        with profile_stage("mixer " + getattr(self.mixer, "kind", "?")):
+            branches = self._run(self.mixer, "y", u, step, view)
+        if self.ffn is None:
+            with profile_stage("norm"):
+                self._join(branches, self.vec1, resid, nxt, nxt_out)
+        else:
+            g = self.scratch(step, "normed_mid", (N, H), step.dtype)
+            with profile_stage("norm"):
+                self._join(branches, self.vec1, resid, self.ffn_norm, g)
+            with profile_stage("feed_forward " + getattr(self.ffn, "kind", "?")):
+                branches = self._run(self.ffn, "y", g, step)
+            with profile_stage("norm"):
+                self._join(branches, self.vec2, resid, nxt, nxt_out)
+        if nxt is not None:
+            step.handed = (nxt, nxt_out)
+
+
 @register("block", "postnorm")
 class PostNormBlock(Part):
     """x += norm1(mixer(x)); then, if the layer has a feed-forward, x += norm2(feed_forward(x)): the norms sit on

@@ -66,6 +66,8 @@ class ClampedGLU(Part):
     gelu (1.702).  Gate and up are one product (the two matrices end to end); the activation is computed in
     float32 from its float32 results."""
 
+    overwrites = True            # forward(..., accumulate=False) writes its result instead of adding it
+
     def __init__(self, hidden: int, ff: int, limit: float, alpha: float = 1.702):
         self.hidden, self.ff, self.limit, self.alpha = int(hidden), int(ff), float(limit), float(alpha)
 
@@ -80,13 +82,13 @@ class ClampedGLU(Part):
         self.w_gu = torch.cat([wg, wu], dim=0).contiguous()
         self.w_down = t["down"]
 
-    def forward(self, g, resid, step) -> None:
+    def forward(self, g, resid, step, accumulate: bool = True) -> None:
         N = g.shape[0]
         gu = self.scratch(step, "proj", (N, 2 * self.ff), torch.float32)
         linear(g, self.w_gu, gu)
         h = self.scratch(step, "ffh", (N, self.ff), step.dtype)
         K.glu_clamped(gu, h, self.limit, self.alpha)
-        linear(h, self.w_down, resid, accumulate=True)
+        linear(h, self.w_down, resid, accumulate=accumulate)
 
 
 @register("feed_forward", "routed_experts")

@@ -308,15 +308,28 @@ class SinkAttention(Part):
     and softmax are float32.  ``norm_per_head``: the q and k norms run over every head by itself, with one
     weight [key_dim] shared by the heads.  ``chunk`` c > 0 (instead of a window): token i reads token j <= i
     only if i // c == j // c, chunks counted from the sequence's first position.  A position part with an
-    ``amplitude()`` has its cos and sin multiplied by it."""
+    ``amplitude()`` has its cos and sin multiplied by it.
+
+    Further options.  ``talk``: the heads' softmax weights are mixed after the softmax, w'_h(i, j) =
+    sum_g T[h, g] w_g(i, j) with the tensor ``talk`` [heads, heads], and head h applies w'_h to the values of its own
+    kv head (computed as sum_g T[h, g] O[g, kv(h)] from every head's weights applied to every kv head's values).
+    ``conv`` k > 0: q and k pass a causal convolution of k taps per channel (``q.conv``, ``k.conv``, no bias, no
+    activation, the last tap the current token's) directly after their projections; the last k - 1 projected rows
+    are part of a sequence's state.  ``values_are_keys``: there is no value projection, the values are the first
+    ``value_dim`` elements of the keys as they are cached.  ``distance_bias``: r1_h ln(1 + r2_h (i - j)) is taken off
+    the scores (``r1``, ``r2`` [heads]).  ``sink`` "zero": the sink's score is 0 for every head and there is no
+    tensor (the denominator gains 1).  ``gated`` "element": the gate is one projection of the layer's input per
+    element of the concatenated heads.  ``split_weights``: steps of many tokens carry 16 instead of 8 bits of a
+    softmax weight's mantissa into the value product."""
 
     nested_roles = {"position": "position"}
     overwrites = True            # forward(..., accumulate=False) writes its result instead of adding it
 
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, scale: float,
                  position, softcap: float = 0.0, window: int = 0, keep_first: int = 0,
-                 qk_norm_eps: Optional[float] = None, sink: bool = True, gated: bool = True,
-                 norm_per_head: bool = False, chunk: int = 0):
+                 qk_norm_eps: Optional[float] = None, sink=True, gated=True,
+                 norm_per_head: bool = False, chunk: int = 0, talk: bool = False, conv: int = 0,
+                 values_are_keys: bool = False, distance_bias: bool = False, split_weights: bool = False):
         if n_kv_heads < 1 or n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
         if not (1 <= key_dim <= K.MAX_HEAD_DIM and 1 <= value_dim <= K.MAX_HEAD_DIM):
@@ -325,8 +338,18 @@ class SinkAttention(Part):
         self.dk, self.dv, self.scale, self.softcap = int(key_dim), int(value_dim), float(scale), float(softcap or 0.0)
         self.window, self.keep_first = int(window), int(keep_first) if window else 0
         self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
-        self.sink, self.gated, self.position = bool(sink), bool(gated), position
+        if sink not in (True, False, "zero") or gated not in (True, False, "element"):
+            raise ValueError(f"sink {sink!r} (True, False or 'zero'), gated {gated!r} (True, False or 'element')")
+        self.sink, self.gated, self.position = sink, gated, position
         self.norm_per_head, self.chunk = bool(norm_per_head), int(chunk)
+        self.talk, self.conv, self.values_are_keys = bool(talk), int(conv), bool(values_are_keys)
+        self.distance_bias, self.split_weights = bool(distance_bias), bool(split_weights)
+        if self.values_are_keys and self.dv > self.dk:
+            raise ValueError(f"values of {self.dv} cannot be the first elements of keys of {self.dk}")
+        if not 0 <= self.conv <= K.MAX_CONV_K:
+            raise ValueError(f"convolution width {self.conv} is outside 0..{K.MAX_CONV_K}")
+        if self.conv and not self.values_are_keys:
+            raise ValueError("convolved q and k come with values that are the keys (a value projection beside them is not built)")
         if self.chunk < 0 or (self.chunk and self.window):
             raise ValueError("a chunked mask is a size > 0 and comes instead of a window")
         self.rot_dims = 0
@@ -342,45 +365,74 @@ class SinkAttention(Part):
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         H, nh, nkv, dk, dv = self.hidden, self.nh, self.nkv, self.dk, self.dv
-        specs = {"q": ParamSpec((nh * dk, H)), "k": ParamSpec((nkv * dk, H)), "v": ParamSpec((nkv * dv, H)),
-                 "o": ParamSpec((H, nh * dv))}
+        specs = {"q": ParamSpec((nh * dk, H)), "k": ParamSpec((nkv * dk, H))}
+        if not self.values_are_keys:
+            specs["v"] = ParamSpec((nkv * dv, H))
+        specs["o"] = ParamSpec((H, nh * dv))
         if self.qk_norm_eps is not None:
             specs["q.norm"] = ParamSpec((dk if self.norm_per_head else nh * dk,), "vector", "norm")
             specs["k.norm"] = ParamSpec((dk if self.norm_per_head else nkv * dk,), "vector", "norm")
-        if self.sink:
+        if self.sink is True:
             specs["sink"] = ParamSpec((nh,), "vector", "bias")
         if self.gated:
-            specs["g"] = ParamSpec((nh, H))
+            specs["g"] = ParamSpec((nh * dv if self.gated == "element" else nh, H))
+        if self.talk:
+            specs["talk"] = ParamSpec((nh, nh), "vector", "conv")
+        if self.conv:
+            specs["q.conv"] = ParamSpec((nh * dk, self.conv), "vector", "conv")
+            specs["k.conv"] = ParamSpec((nkv * dk, self.conv), "vector", "conv")
+        if self.distance_bias:
+            specs["r1"] = ParamSpec((nh,), "vector", "norm")
+            specs["r2"] = ParamSpec((nh,), "vector", "norm")
         return specs
 
     def load(self, t) -> None:
-        self.w_qkvg = _fuse_rows([t["q"], t["k"], t["v"]] + ([t["g"]] if self.gated else []))
+        self.w_qkvg = _fuse_rows([t["q"], t["k"]] + ([] if self.values_are_keys else [t["v"]]) + ([t["g"]] if self.gated else []))
         self.w_o = t["o"]
         self.q_norm, self.k_norm, self.sinks = t.get("q.norm"), t.get("k.norm"), t.get("sink")
+        if self.sink == "zero":
+            self.sinks = torch.zeros(self.nh, dtype=torch.float32, device=self.w_o.device)
+        self.w_talk = t["talk"].float().contiguous() if self.talk else None
+        self.taps = torch.cat([t["q.conv"], t["k.conv"]], dim=0).contiguous() if self.conv else None
+        self.bias = (t["r1"].float().contiguous(), t["r2"].float().contiguous()) if self.distance_bias else None
 
     def cache_need(self):
-        return KVNeed(self.nkv, self.dk, self.window, 0 if self.dv == self.dk else self.dv, self.keep_first, self.chunk)
+        kv = KVNeed(self.nkv, self.dk, self.window, self.dv if self.values_are_keys or self.dv != self.dk else 0,
+                    self.keep_first, self.chunk, values_in_keys=self.values_are_keys)
+        return [kv, StateNeed((self.conv - 1, (self.nh + self.nkv) * self.dk))] if self.conv > 1 else kv
 
     def forward(self, u, resid, step, view, accumulate: bool = True) -> None:
         N = u.shape[0]
         nh, nkv, dk, dv = self.nh, self.nkv, self.dk, self.dv
+        conv_state = None
+        if self.conv > 1:
+            view, conv_state = view[0], view[1].state
         proj = self.scratch(step, "proj", (N, self.w_qkvg.shape[0]), torch.float32)
         linear(u, self.w_qkvg, proj)
         rot = self.position.rotary(u.device) if self.rot_dims else None
         q = self.scratch(step, "q", (N, nh * dk), step.dtype)
-        K.qkv_prepare_wide(proj, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.rot_dims,
+        rows = proj
+        if self.conv:
+            rows = self.scratch(step, "qk", (N, (nh + nkv) * dk), torch.float32)
+            K.causal_conv(proj[:, :(nh + nkv) * dk], self.taps, None, conv_state, step.seq_of, step.cu, step.slots, rows,
+                          step.n_seqs)
+        K.qkv_prepare_wide(rows, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.rot_dims,
                            rot[0] if rot is not None else None, step.positions, step.seq_of, view.page_table,
-                           view.pool, view.page_size, q, nh, nkv, dk, dv, per_head=self.norm_per_head,
+                           view.pool, view.page_size, q, nh, nkv, dk, 0 if self.values_are_keys else dv,
+                           per_head=self.norm_per_head,
                            amplitude=float(getattr(self.position, "amplitude", lambda: 1.0)()) if self.rot_dims else 1.0)
         o = self.scratch(step, "mix", (N, nh * dv), step.dtype)
-        g0 = nh * dk + nkv * (dk + dv)
+        g0 = nh * dk + nkv * dk + (0 if self.values_are_keys else nkv * dv)
+        wide = self.gated == "element"
         extras = dict(softcap=self.softcap, window=self.window, keep_first=self.keep_first, sinks=self.sinks,
-                      gate=proj[:, g0:g0 + nh] if self.gated else None, chunk=self.chunk)
+                      gate=proj[:, g0:g0 + (nh * dv if wide else nh)] if self.gated else None, chunk=self.chunk,
+                      distance_bias=self.bias, values_in_keys=self.values_are_keys, gate_wide=wide,
+                      out_all=self.scratch(step, "o_all", (N, nh, nkv, dv), torch.float32) if self.talk else None)
         # few query tokens, or many sequences with a token or two each: every query token on its own
         few = N <= K.DECODE_ATTENTION_MAX_TOKENS or step.max_len <= K.DECODE_ATTENTION_MAX_QUERIES
         if not few and K.attention_sink_prefill_supported(step.dtype, dk, dv):
             K.attention_sink_prefill(q, view.pool, view.page_size, view.page_table, step.cu, step.starts, o,
-                                     step.n_seqs, nh, nkv, dk, dv, self.scale, **extras)
+                                     step.n_seqs, nh, nkv, dk, dv, self.scale, split_weights=self.split_weights, **extras)
         else:
             K.attention_sink(q, view.pool, view.page_size, view.page_table, step.positions, step.seq_of, o, nh, nkv,
                              dk, dv, self.scale, **extras)
@@ -391,8 +443,11 @@ class SinkAttention(Part):
             # keys and values: every query reads its own in a step of few tokens, a sequence's tile shares them otherwise
             rows = pairs if few else sum(min(s + n, n + reach) if reach else s + n
                                          for s, n in zip(step.host_starts, step.host_lens))
-            K.account(nkv * (dk + dv) * view.pool.element_size() * rows + N * nh * (dk + dv) * q.element_size(),
-                      2 * nh * (dk + dv) * pairs)
+            vh = nkv if self.talk else 1          # mixed weights: every head's weights meet every kv head's values
+            K.account(nkv * (dk + dv) * view.pool.element_size() * rows + N * nh * (dk + dv * vh) * q.element_size(),
+                      2 * nh * (dk + dv) * vh * pairs)
+        if self.talk:
+            K.mix_heads(extras["out_all"], self.w_talk, o, nh, nkv, dv)
         linear(o, self.w_o, resid, accumulate=accumulate)
 
 
@@ -802,4 +857,134 @@ class ChannelDelta(Part):
                      q_scale=dk ** -0.5, norm_eps=self.UNIT_EPS, max_len=step.max_len, ws=step.ws)
         y = self.scratch(step, "mix", (N, vv), step.dtype)
         K.gated_rmsnorm(o, up[:, hk:hk + vv], self.norm, dv, self.eps, K.GATE_SIGMOID, y)
+        linear(y, self.w_o, resid, accumulate=accumulate)
+
+
+@register("mixer", "gated_recurrence")
+class GatedRecurrence(Part):
+    """A recurrent block around a real-gated linear recurrent unit (De et al., "Griffin: Mixing Gated Linear
+    Recurrences with Local Attention for Efficient Language Models"): two branches of ``width`` channels,
+    y = gelu_tanh(W_y h + b_y) and u = conv(W_x h + b_x), a causal convolution of ``conv`` taps per channel with a
+    bias and no activation (the last tap the current token's); u cut into ``blocks`` equal parts, in part b
+    r = sigmoid(A_b u_b + a_b) and i = sigmoid(B_b u_b + b_b) with square matrices [out, in];
+    log a = -``c`` r softplus(lam), S_t = a S_(t-1) + sqrt(1 - a^2) i u from S = 0 (the first token is no special
+    case); the result is W_o (S * y).  S [width] and the convolution's last conv - 1 inputs are float32 per sequence
+    and start at zero; gates, decays, state and sums are float32 in every run."""
+
+    overwrites = True
+
+    def __init__(self, hidden: int, width: int, blocks: int, conv: int, c: float = 8.0):
+        if blocks < 1 or width % blocks:
+            raise ValueError(f"{width} channels do not split into {blocks} equal parts")
+        if not 1 <= conv <= K.MAX_CONV_K:
+            raise ValueError(f"convolution width {conv} is outside 1..{K.MAX_CONV_K}")
+        self.hidden, self.width, self.blocks, self.conv, self.c = int(hidden), int(width), int(blocks), int(conv), float(c)
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        H, C, nb = self.hidden, self.width, self.blocks
+        bs = C // nb
+        return {"y": ParamSpec((C, H)), "y.b": ParamSpec((C,), "vector", "bias"),
+                "x": ParamSpec((C, H)), "x.b": ParamSpec((C,), "vector", "bias"),
+                "conv": ParamSpec((C, self.conv), "vector", "conv"), "conv.b": ParamSpec((C,), "vector", "bias"),
+                "ra": ParamSpec((nb, bs, bs), "vector", "linear"), "ra.b": ParamSpec((nb, bs), "vector", "bias"),
+                "ri": ParamSpec((nb, bs, bs), "vector", "linear"), "ri.b": ParamSpec((nb, bs), "vector", "bias"),
+                "lam": ParamSpec((C,), "vector", "norm"), "o": ParamSpec((H, C))}
+
+    def load(self, t) -> None:
+        self.w_yx = _fuse_rows([t["y"], t["x"]])
+        b = torch.cat([t["y.b"].float(), t["x.b"].float()])
+        self.b_yx = torch.cat([b, b.new_zeros(self.w_yx.shape[0] - b.numel())]).contiguous()
+        self.taps, self.b_conv = t["conv"].contiguous(), t["conv.b"]
+        # the parts' matrices transposed to [in, out]: the gate kernel's threads read consecutive outputs
+        self.wa_t = t["ra"].float().transpose(1, 2).contiguous()
+        self.wi_t = t["ri"].float().transpose(1, 2).contiguous()
+        self.ba, self.bi = t["ra.b"].float().reshape(-1).contiguous(), t["ri.b"].float().reshape(-1).contiguous()
+        self.lam, self.w_o = t["lam"], t["o"]
+
+    def cache_need(self):
+        needs = [StateNeed((self.width,))]
+        if self.conv > 1:
+            needs.append(StateNeed((self.conv - 1, self.width)))
+        return needs
+
+    def forward(self, u, resid, step, view, accumulate: bool = True) -> None:
+        N, C = u.shape[0], self.width
+        memory = view[0]
+        conv_state = view[1].state if self.conv > 1 else None
+        proj = self.scratch(step, "proj", (N, self.w_yx.shape[0]), torch.float32)
+        linear(u, self.w_yx, proj, bias=self.b_yx)
+        uc = self.scratch(step, "u", (N, C), torch.float32)
+        K.causal_conv(proj[:, C:2 * C], self.taps, self.b_conv, conv_state, step.seq_of, step.cu, step.slots, uc, step.n_seqs)
+        a = self.scratch(step, "a", (N, C), torch.float32)
+        x = self.scratch(step, "x", (N, C), torch.float32)
+        K.block_gates(uc, self.wa_t, self.wi_t, self.ba, self.bi, self.lam, self.c, a, x)
+        g = self.scratch(step, "mix", (N, C), step.dtype)
+        K.gated_recurrence(a, x, proj[:, :C], memory.state, step.slots, step.cu, g, step.n_seqs, max_len=step.max_len)
+        linear(g, self.w_o, resid, accumulate=accumulate)
+
+
+@register("mixer", "gated_delta")
+class GatedDeltaRule(Part):
+    """The gated delta rule with one decay per head (Yang, Kautz and Hatamizadeh, "Gated Delta Networks: Improving
+    Mamba2 with Delta Rule"): q = W_q h and k = W_k h on ``kv_heads`` heads of ``key_dim``, v = W_v h on ``n_heads``
+    heads of ``value_dim`` (head h reads q/k head h // (n_heads / kv_heads)); each passes a causal convolution of
+    ``conv`` taps per channel (no bias, the last tap the current token's) and silu; q and k become unit vectors per
+    head (x / sqrt(sum x^2 + 1e-6)), q times key_dim^-1/2; beta = sigmoid(W_b h) and
+    g = exp(-exp(A_log_h) softplus(W_a h + dt_bias)) per head; per head S <- g S; u = beta (v - S^T k);
+    S <- S + k u^T; o = S^T q; each head's o over its root mean square, times ``norm`` [value_dim], times
+    silu(W_g h); then W_o.  The state [heads, value_dim, key_dim] and the convolution's last conv - 1 inputs are
+    float32 per sequence and start at zero; decays, beta, unit norms, state and sums are float32 in every run."""
+
+    overwrites = True
+    UNIT_EPS = 1e-6
+
+    def __init__(self, hidden: int, n_heads: int, kv_heads: int, key_dim: int, value_dim: int, conv: int, eps: float):
+        if kv_heads < 1 or n_heads % kv_heads:
+            raise ValueError(f"{n_heads} heads are not a multiple of {kv_heads} kv heads")
+        if not 1 <= key_dim <= K.MAX_SCAN_KEY_DIM:
+            raise ValueError(f"key size {key_dim} is outside 1..{K.MAX_SCAN_KEY_DIM}")
+        if not 1 <= conv <= K.MAX_CONV_K:
+            raise ValueError(f"convolution width {conv} is outside 1..{K.MAX_CONV_K}")
+        self.hidden, self.nh, self.nkv, self.dk, self.dv = int(hidden), int(n_heads), int(kv_heads), int(key_dim), int(value_dim)
+        self.conv, self.eps = int(conv), float(eps)
+        self.channels = 2 * self.nkv * self.dk + self.nh * self.dv
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        H, qk, vv, c = self.hidden, self.nkv * self.dk, self.nh * self.dv, self.conv
+        return {"q": ParamSpec((qk, H)), "q.conv": ParamSpec((qk, c), "vector", "conv"),
+                "k": ParamSpec((qk, H)), "k.conv": ParamSpec((qk, c), "vector", "conv"),
+                "v": ParamSpec((vv, H)), "v.conv": ParamSpec((vv, c), "vector", "conv"),
+                "b": ParamSpec((self.nh, H)), "a": ParamSpec((self.nh, H)),
+                "A_log": ParamSpec((self.nh,), "vector", "bias"), "dt_bias": ParamSpec((self.nh,), "vector", "bias"),
+                "norm": ParamSpec((self.dv,), "vector", "norm"), "g": ParamSpec((vv, H)), "o": ParamSpec((H, vv))}
+
+    def load(self, t) -> None:
+        # one product: [q | k | v | gate | beta | decay]
+        self.w_in = _fuse_rows([t["q"], t["k"], t["v"], t["g"], t["b"], t["a"]])
+        self.taps = torch.cat([t["q.conv"], t["k.conv"], t["v.conv"]], dim=0).contiguous()
+        self.a_log, self.dt_bias, self.norm, self.w_o = t["A_log"], t["dt_bias"], t["norm"], t["o"]
+
+    def cache_need(self):
+        needs = [StateNeed((self.nh, self.dv, self.dk))]
+        if self.conv > 1:
+            needs.append(StateNeed((self.conv - 1, self.channels)))
+        return needs
+
+    def forward(self, u, resid, step, view, accumulate: bool = True) -> None:
+        N = u.shape[0]
+        nh, nkv, dk, dv, C = self.nh, self.nkv, self.dk, self.dv, self.channels
+        qk, vv = nkv * dk, nh * dv
+        memory = view[0]
+        conv_state = view[1].state if self.conv > 1 else None
+        proj = self.scratch(step, "proj", (N, self.w_in.shape[0]), torch.float32)
+        linear(u, self.w_in, proj)
+        xbc = self.scratch(step, "xbc", (N, C), torch.float32)
+        K.causal_conv_silu(proj[:, :C], self.taps, None, conv_state, step.seq_of, step.cu, step.slots, xbc, step.n_seqs)
+        b0 = C + vv
+        o = self.scratch(step, "o", (N, vv), torch.float32)
+        K.delta_scan(xbc[:, :qk], xbc[:, qk:2 * qk], xbc[:, 2 * qk:], proj[:, b0:b0 + nh], proj[:, b0 + nh:b0 + 2 * nh],
+                     self.dt_bias, self.a_log, memory.state, step.slots, step.cu, o, step.n_seqs, nh, nkv, dk, dv,
+                     q_scale=dk ** -0.5, norm_eps=self.UNIT_EPS, max_len=step.max_len, ws=step.ws, head_decay=True)
+        y = self.scratch(step, "mix", (N, vv), step.dtype)
+        K.gated_rmsnorm(o, proj[:, C:C + vv], self.norm, dv, self.eps, K.GATE_SILU, y)
         linear(y, self.w_o, resid, accumulate=accumulate)

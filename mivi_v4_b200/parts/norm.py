@@ -14,14 +14,18 @@ from .spec import ParamSpec
 @register("norm", "rmsnorm")
 class RMSNorm(Part):
     """y = x * (mean(x^2) + eps)^-1/2 * weight over the last dimension, in
-    float32 (crates/mivi-core/src/simd/norm.rs:38-72; math.rs:14-29)."""
+    float32 (crates/mivi-core/src/simd/norm.rs:38-72; math.rs:14-29).  ``one_plus``: the checkpoint stores the
+    weight around zero and the factor is 1 + weight (added once, in float32, when the weights are loaded)."""
 
-    def __init__(self, dim: int, eps: float):
-        self.dim, self.eps = int(dim), float(eps)
+    def __init__(self, dim: int, eps: float, one_plus: bool = False):
+        self.dim, self.eps, self.one_plus = int(dim), float(eps), bool(one_plus)
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.dim,), "vector", "norm")}
+        return {"weight": ParamSpec((self.dim,), "vector", "bias" if self.one_plus else "norm")}
+
+    def load(self, t) -> None:
+        self.weight = (t["weight"].float() + 1.0).contiguous() if self.one_plus else t["weight"]
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         return K.rmsnorm(x, self.weight, self.eps, out, rows)
