@@ -239,3 +239,14 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], rnd:
             layers_out.append(x.clone())
     f = rms_norm(x, weights["final.norm"], eps, one_plus=True)
     return _r(f, rnd) @ E.T
+
+
+def greedy(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], n: int) -> List[int]:
+    """The n tokens that follow ``tokens`` when the largest logit is taken each time (the whole sequence is run
+    again for every token: the slow form)."""
+    seq, out = list(tokens), []
+    for _ in range(n):
+        t = int(forward(cfg, weights, seq)[-1].argmax())
+        seq.append(t)
+        out.append(t)
+    return out
