@@ -80,6 +80,50 @@ def window_mask(T: int, window: int):
     return seen
 
 
+# ---- softmax weights of grouped heads -----------------------------------------------------------------------------
+def attention_weights(q, k, scale, positions=None, window=0, cap=0.0, bias=None, sink=False, rnd: Round = None):
+    """q [N, H, d] at ``positions`` (None: 0 .. N-1) over the keys k [T, G, d] at positions 0 .. T-1 (head h reads
+    key head h // (H / G)): weights [H, N, T].  score = (q . k) * scale; capped as cap tanh(score / cap) if cap > 0;
+    minus bias[0]_h ln(1 + bias[1]_h (i - j)) if there is a bias; key j is seen from i if 0 <= i - j (< window, if
+    there is one); softmax over the seen keys, with ``sink`` one more term exp(0) in the denominator."""
+    N, H, _ = q.shape
+    T, G, _ = k.shape
+    pos = torch.arange(N) if positions is None else torch.as_tensor(positions)
+    kv_of = torch.arange(H) // (H // G)
+    s = torch.einsum("nhd,shd->hns", _r(q, rnd), _r(k, rnd)[:, kv_of]) * scale
+    if cap:
+        s = cap * torch.tanh(s / cap)
+    dist = pos[:, None] - torch.arange(T)[None, :]
+    if bias is not None:
+        r1, r2 = bias[0].to(F)[:, None, None], bias[1].to(F)[:, None, None]
+        s = s - r1 * torch.log1p(r2 * dist.clamp(min=0).to(F)[None])
+    seen = dist >= 0
+    if window:
+        seen = seen & (dist < window)
+    s = s.masked_fill(~seen[None], -math.inf)
+    mx = s.max(-1).values
+    if sink:
+        mx = torch.clamp(mx, min=0.0)
+    e = torch.exp(s - mx[..., None])
+    den = e.sum(-1)
+    if sink:
+        den = den + torch.exp(-mx)
+    return e / den[..., None]
+
+
+def apply_weights(w, v, rnd: Round = None):
+    """w [H, N, T], v [T, G, dv]: every head's weighted sum of the values of its own key/value head, [N, H * dv]."""
+    H, N, _ = w.shape
+    G = v.shape[1]
+    kv_of = torch.arange(H) // (H // G)
+    return torch.einsum("hns,shd->nhd", w, _r(v, rnd)[:, kv_of]).reshape(N, -1)
+
+
+def mix_heads(w, talk):
+    """w'_h(i, j) = sum_g talk[h, g] w_g(i, j)."""
+    return torch.einsum("hg,gns->hns", talk.to(F), w)
+
+
 # ---- attention with mixed heads (the left side of a parallel mixer) ---------------------------------------------
 def talking_attention(h, p: Dict[str, torch.Tensor], m: dict, eps: float, rnd: Round = None):
     """h [T, width] of one sequence from position 0.  Norm over the whole q and k projections, rotation of a part
@@ -94,17 +138,10 @@ def talking_attention(h, p: Dict[str, torch.Tensor], m: dict, eps: float, rnd: R
     rot = m.get("rot") or {"base": 1.0, "dims": 0}
     q = rotate_half(q, pos, rot["base"], rot["dims"])
     k = rotate_half(k, pos, rot["base"], rot["dims"])
-    kv_of = torch.arange(H) // (H // G)
-    s = torch.einsum("thd,shd->hts", _r(q, rnd), _r(k, rnd)[:, kv_of]) * m["scale"]
-    cap = m.get("softcap")
-    if cap:
-        s = cap * torch.tanh(s / cap)
-    s = s.masked_fill(~window_mask(T, (m.get("mask") or {}).get("size", 0))[None], -math.inf)
-    w = torch.softmax(s, dim=-1)                                         # [H, T, T]
+    w = attention_weights(q, k, m["scale"], window=(m.get("mask") or {}).get("size", 0), cap=m.get("softcap") or 0.0, rnd=rnd)
     if "talk" in p:
-        w = torch.einsum("hg,gts->hts", p["talk"].to(F), w)
-    o = torch.einsum("hts,shd->thd", w, _r(v, rnd)[:, kv_of]).reshape(T, H * vd)
-    return _lin(o, p["o"], rnd)
+        w = mix_heads(w, p["talk"])
+    return _lin(apply_weights(w, v, rnd), p["o"], rnd)
 
 
 # ---- the recurrent block with a real-gated linear recurrent unit (the right side) -------------------------------
@@ -151,18 +188,9 @@ def distance_attention(h, p: Dict[str, torch.Tensor], m: dict, rnd: Round = None
     H, G, d, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = causal_conv(_lin(h, p["q"], rnd), p["q.conv"]).view(T, H, d)
     k = causal_conv(_lin(h, p["k"], rnd), p["k.conv"]).view(T, G, d)
-    v = k[..., :vd]
-    kv_of = torch.arange(H) // (H // G)
-    s = torch.einsum("thd,shd->hts", _r(q, rnd), _r(k, rnd)[:, kv_of]) * m["scale"]
-    pos = torch.arange(T)
-    dist = (pos[:, None] - pos[None, :]).clamp(min=0).to(F)
-    s = s - p["r1"].to(F)[:, None, None] * torch.log1p(p["r2"].to(F)[:, None, None] * dist[None])
-    s = s.masked_fill(~window_mask(T, (m.get("mask") or {}).get("size", 0))[None], -math.inf)
-    mx = torch.clamp(s.max(-1).values, min=0.0)
-    e = torch.exp(s - mx[..., None])
-    w = e / (e.sum(-1) + torch.exp(-mx))[..., None]                      # one more term in the denominator: exp(0)
-    o = torch.einsum("hts,shd->thd", w, _r(v, rnd)[:, kv_of]).reshape(T, H * vd)
-    o = o * torch.sigmoid(_lin(h, p["g"], rnd))
+    w = attention_weights(q, k, m["scale"], window=(m.get("mask") or {}).get("size", 0), bias=(p["r1"], p["r2"]), sink=True,
+                          rnd=rnd)
+    o = apply_weights(w, k[..., :vd], rnd) * torch.sigmoid(_lin(h, p["g"], rnd))
     return _lin(o, p["o"], rnd)
 
 
@@ -182,17 +210,25 @@ def delta_rule(q, k, v, beta, g):
     return out
 
 
+def unit(x, eps: float = 1e-6):
+    return x / torch.sqrt((x * x).sum(-1, keepdim=True) + eps)
+
+
+def head_decay(a, dt_bias, a_log):
+    """g = exp(-exp(A_log) softplus(a + dt_bias)), one a head."""
+    return torch.exp(-torch.exp(a_log.to(F)) * softplus(a + dt_bias.to(F)))
+
+
 def delta_mixer(h, p: Dict[str, torch.Tensor], m: dict, eps: float, rnd: Round = None):
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = silu(causal_conv(_lin(h, p["q"], rnd), p["q.conv"])).view(T, G, dk)
     k = silu(causal_conv(_lin(h, p["k"], rnd), p["k.conv"])).view(T, G, dk)
     v = silu(causal_conv(_lin(h, p["v"], rnd), p["v.conv"])).view(T, H, dv)
-    q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
-    k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    q, k = unit(q) * dk ** -0.5, unit(k)
     kv_of = torch.arange(H) // (H // G)
     beta = torch.sigmoid(_lin(h, p["b"], rnd))
-    g = torch.exp(-torch.exp(p["A_log"].to(F)) * softplus(_lin(h, p["a"], rnd) + p["dt_bias"].to(F)))
+    g = head_decay(_lin(h, p["a"], rnd), p["dt_bias"], p["A_log"])
     o = delta_rule(q[:, kv_of], k[:, kv_of], v, beta, g)
     o = rms_norm(o, p["norm"], eps) * silu(_lin(h, p["g"], rnd)).view(T, H, dv)
     return _lin(o.reshape(T, H * dv), p["o"], rnd)
