@@ -10,6 +10,7 @@ prefill, then generation timed without its first token).
     python bench.py --design votavik [--stages ..]      (the Votavik decoder beside the LFM2 model of equal sizes)
     python bench.py --design tevirax [--stages ..]      (the Tevirax decoder beside the Votavik decoder of equal sizes)
     python bench.py --design puzorax [--stages ..]      (the Puzorax decoder beside the Tevirax decoder of equal sizes)
+    python bench.py --design ropelix [--stages ..]      (the Ropelix decoder beside the Tevirax decoder of equal sizes)
     python bench.py --kernel NAME [--m .. --n .. --k ..] (one kernel alone, for timing and for profilers)
 
 One "step" is one decode step of the whole batch.  Prints ONE JSON line:
@@ -247,6 +248,23 @@ def puzorax_config(width, layers, heads, kv_heads, ff, vocab):
                         "mixer": latent if i % 3 == 2 else delta, "mlp": moe} for i in range(n)]}
 
 
+def ropelix_config(width, layers, heads, kv_heads, ff, vocab):
+    """A layer of attention with mixed heads beside a gated linear recurrence, then a layer of attention with convolved
+    q and k whose values are its keys, then a delta-rule layer, and so on; every layer carries a dense clamped
+    feed-forward.  The side-by-side attention has a quarter of the kv heads (every head's weights meet every kv
+    head's values there)."""
+    left = {"heads": heads, "kv_heads": max(1, kv_heads // 4), "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 50.0,
+            "mask": {"size": 1024}, "rot": {"dims": 32, "base": 1000000.0}}
+    par = {"left": left, "right": {"width": width, "blocks": max(1, width // 256), "conv": 4}, "left_scale": 0.6, "right_scale": 0.5}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "conv": 3, "scale": 0.125, "mask": {"size": 1024}}
+    delta = {"heads": max(1, width // 128), "kv_heads": max(1, width // 256), "dim": 128, "vdim": 128, "conv": 4}
+    kinds = (("parallel", par), ("attention", att), ("delta", delta))
+    return {"architecture": "Ropelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": float(width) ** 0.5},
+            "residual_mult": 0.7,
+            "layers": [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}}
+                       for i in range(layers)]}
+
+
 def lfm2_like(width, layers, heads, kv_heads, ff, vocab):
     cfg = dict(BENCH_CONFIG)
     cfg.update(hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv_heads,
@@ -257,15 +275,17 @@ def lfm2_like(width, layers, heads, kv_heads, ff, vocab):
 
 def run_design(args, warmup: int) -> int:
     """Prefill and decode throughput of a further design (--design) at the sizes of DESIGN_SIZES, each beside its
-    closest neighbour in the library at equal sizes (Votavik beside LFM2, Tevirax beside Votavik, Puzorax beside Tevirax), random weights,
+    closest neighbour in the library at equal sizes (Votavik beside LFM2, Tevirax beside Votavik, Puzorax and Ropelix beside
+    Tevirax), random weights,
     bfloat16: one JSON line.  With --stages: where a step of the design's model (--size) goes, kernel by kernel."""
     import torch
     from mivi_v4_b200 import measure, random_model
     pk, pk_src = peaks()
     # the design that was asked for, beside its closest neighbour in the library at equal sizes
-    design_cfg = {"votavik": votavik_config, "tevirax": tevirax_config, "puzorax": puzorax_config}[args.design]
+    design_cfg = {"votavik": votavik_config, "tevirax": tevirax_config, "puzorax": puzorax_config,
+                  "ropelix": ropelix_config}[args.design]
     beside, beside_cfg = {"votavik": ("lfm2", lfm2_like), "tevirax": ("votavik", votavik_config),
-                          "puzorax": ("tevirax", tevirax_config)}[args.design]
+                          "puzorax": ("tevirax", tevirax_config), "ropelix": ("tevirax", tevirax_config)}[args.design]
     if args.stages:
         model = random_model(design_cfg(*DESIGN_SIZES[args.size]), seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
         lens = [args.tokens] if args.stages == "prefill" else [args.prompt_len] * args.batch
@@ -386,7 +406,7 @@ def main() -> int:
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="run one of the two further workloads instead of the default benchmark")
     ap.add_argument("--size", default="w2048", choices=sorted(DESIGN_SIZES), help="with --design --stages: which size")
-    ap.add_argument("--design", default=None, choices=["votavik", "tevirax", "puzorax"],
+    ap.add_argument("--design", default=None, choices=["votavik", "tevirax", "puzorax", "ropelix"],
                     help="measure a further design beside its closest neighbour in the library at equal sizes (Votavik beside LFM2, "
                          "Tevirax beside Votavik) instead of the default benchmark")
     ap.add_argument("--stages", default=None, choices=["decode", "prefill"],

@@ -398,11 +398,50 @@ mix_heads_kernel(const float* __restrict__ o_all, const float* __restrict__ talk
     out[idx] = mv_from_f32<T>(acc);
 }
 
+// The same with a block a token: the token's nh * nkv * dv values and the mixing matrix lie in shared memory, so that
+// every value is read from memory once although nh / nkv heads sum it.
+template <typename T>
+__global__ void __launch_bounds__(256)
+mix_heads_token_kernel(const float* __restrict__ o_all, const float* __restrict__ talk, T* __restrict__ out, int nh,
+                       int nkv, int dv) {
+    mv_pdl_begin();
+    extern __shared__ __align__(16) float mh_smem[];
+    float* vals = mh_smem;                                  // [nh][nkv][dv]
+    float* tk = vals + (size_t)nh * nkv * dv;               // [nh][nh]
+    const size_t n = blockIdx.x;
+    const int per = nh * nkv * dv;
+    const float* src = o_all + n * per;
+    for (int i = threadIdx.x; i < per; i += blockDim.x) vals[i] = src[i];
+    for (int i = threadIdx.x; i < nh * nh; i += blockDim.x) tk[i] = talk[i];
+    __syncthreads();
+    const int G = nh / nkv;
+    for (int i = threadIdx.x; i < nh * dv; i += blockDim.x) {
+        const int h = i / dv, d = i - h * dv, m = h / G;
+        const float* col = vals + (size_t)m * dv + d;
+        const float* row = tk + (size_t)h * nh;
+        float acc = 0.f;
+        for (int g = 0; g < nh; ++g) acc = fmaf(row[g], col[(size_t)g * nkv * dv], acc);
+        out[n * nh * dv + i] = mv_from_f32<T>(acc);
+    }
+}
+
 MV_API int mv_mix_heads(const float* o_all, const float* talk, void* out, int dtype, int N, int nh, int nkv, int dv,
                         cudaStream_t stream) {
     const long long total = (long long)N * nh * dv;
     if (total <= 0) return 0;
     if (nkv < 1 || nh % nkv) return (int)cudaErrorInvalidValue;
+    const size_t smem = sizeof(float) * ((size_t)nh * nkv * dv + (size_t)nh * nh);
+    // (few tokens: a thread an element fills the device better than a block a token)
+    if (smem <= 96 * 1024 && N >= 128) {
+        if (dtype == MV_DT_BF16) {
+            if (smem > 48 * 1024) cudaFuncSetAttribute(mix_heads_token_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            mv_launch(mix_heads_token_kernel<__nv_bfloat16>, N, 256, smem, stream, o_all, talk, (__nv_bfloat16*)out, nh, nkv, dv);
+        } else {
+            if (smem > 48 * 1024) cudaFuncSetAttribute(mix_heads_token_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            mv_launch(mix_heads_token_kernel<float>, N, 256, smem, stream, o_all, talk, (float*)out, nh, nkv, dv);
+        }
+        return mv_launch_status();
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == MV_DT_BF16)
         mv_launch(mix_heads_kernel<__nv_bfloat16>, blocks, 256, 0, stream, o_all, talk, (__nv_bfloat16*)out, total, nh, nkv, dv);

@@ -13,7 +13,7 @@
 #include "common.cuh"
 
 #define GR_TOK 16            // tokens a block of the gate kernel holds
-#define GR_WARPS 16          // pieces a long sequence is cut into for the walk
+#define GR_WARPS 32          // the most pieces a long sequence is cut into for the walk
 
 __device__ __forceinline__ float gr_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
@@ -70,6 +70,74 @@ block_gates_kernel(const float* __restrict__ u, const float* __restrict__ wa_t, 
     }
 }
 
+// The same for steps of few tokens, where the matrices' bytes are the work: a block is (16 tokens, 32 outputs of one
+// part) and its 8 warps share the part's inputs among them, lane l keeping output l of all 16 tokens for its warp's
+// inputs; the 8 partial sums meet in shared memory and are added in the warps' order.
+#define GR_SPLIT 8
+__global__ void __launch_bounds__(32 * GR_SPLIT)
+block_gates_few_kernel(const float* __restrict__ u, const float* __restrict__ wa_t, const float* __restrict__ wi_t,
+                       const float* __restrict__ ba, const float* __restrict__ bi, const float* __restrict__ lam, float c,
+                       float* __restrict__ a_out, float* __restrict__ x_out, int N, int C, int bs) {
+    mv_pdl_begin();
+    extern __shared__ __align__(16) float gr_us[];           // [bs][GR_TOK], then [GR_SPLIT][2][GR_TOK][32]
+    float* part = gr_us + (size_t)bs * GR_TOK;
+    const int n0 = blockIdx.x * GR_TOK, b = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int o = blockIdx.z * 32 + lane;
+    const int nt = min(GR_TOK, N - n0);
+    for (int idx = threadIdx.x; idx < bs * GR_TOK; idx += blockDim.x) {
+        const int t = idx / bs, in = idx - t * bs;
+        gr_us[in * GR_TOK + t] = t < nt ? u[(size_t)(n0 + t) * C + (size_t)b * bs + in] : 0.f;
+    }
+    __syncthreads();
+    float ar[GR_TOK], ai[GR_TOK];
+#pragma unroll
+    for (int t = 0; t < GR_TOK; ++t) ar[t] = ai[t] = 0.f;
+    const int per = (bs + GR_SPLIT - 1) / GR_SPLIT;
+    const int in0 = warp * per, in1 = min(in0 + per, bs);
+    if (o < bs) {
+        const float* wa = wa_t + (size_t)b * bs * bs + o;
+        const float* wi = wi_t + (size_t)b * bs * bs + o;
+#pragma unroll 8
+        for (int in = in0; in < in1; ++in) {
+            const float x = wa[(size_t)in * bs], y = wi[(size_t)in * bs];
+            const float4* row = reinterpret_cast<const float4*>(gr_us + in * GR_TOK);
+#pragma unroll
+            for (int q = 0; q < GR_TOK / 4; ++q) {
+                const float4 v = row[q];
+                ar[4 * q] = fmaf(x, v.x, ar[4 * q]);         ai[4 * q] = fmaf(y, v.x, ai[4 * q]);
+                ar[4 * q + 1] = fmaf(x, v.y, ar[4 * q + 1]); ai[4 * q + 1] = fmaf(y, v.y, ai[4 * q + 1]);
+                ar[4 * q + 2] = fmaf(x, v.z, ar[4 * q + 2]); ai[4 * q + 2] = fmaf(y, v.z, ai[4 * q + 2]);
+                ar[4 * q + 3] = fmaf(x, v.w, ar[4 * q + 3]); ai[4 * q + 3] = fmaf(y, v.w, ai[4 * q + 3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < GR_TOK; ++t) {
+        part[((warp * 2 + 0) * GR_TOK + t) * 32 + lane] = ar[t];
+        part[((warp * 2 + 1) * GR_TOK + t) * 32 + lane] = ai[t];
+    }
+    __syncthreads();
+    // a thread a (token, output): 16 x 32 pairs over 256 threads
+    for (int idx = threadIdx.x; idx < GR_TOK * 32; idx += blockDim.x) {
+        const int t = idx >> 5, l = idx & 31, oo = blockIdx.z * 32 + l;
+        if (t >= nt || oo >= bs) continue;
+        float sr = 0.f, si = 0.f;
+#pragma unroll
+        for (int w = 0; w < GR_SPLIT; ++w) {
+            sr += part[((w * 2 + 0) * GR_TOK + t) * 32 + l];
+            si += part[((w * 2 + 1) * GR_TOK + t) * 32 + l];
+        }
+        const int ch = b * bs + oo;
+        const float r = 1.0f / (1.0f + expf(-(sr + ba[ch])));
+        const float ig = 1.0f / (1.0f + expf(-(si + bi[ch])));
+        const float log_a = -c * gr_softplus(lam[ch]) * r;
+        const size_t at = (size_t)(n0 + t) * C + ch;
+        a_out[at] = expf(log_a);
+        x_out[at] = sqrtf(-expm1f(2.0f * log_a)) * ig * gr_us[oo * GR_TOK + t];
+    }
+}
+
 MV_API int mv_block_gates(const float* u, const float* wa_t, const float* wi_t, const float* ba, const float* bi,
                           const float* lam, float c, float* a_out, float* x_out, int N, int C, int n_blocks,
                           cudaStream_t stream) {
@@ -77,7 +145,20 @@ MV_API int mv_block_gates(const float* u, const float* wa_t, const float* wi_t, 
     if (n_blocks < 1 || C % n_blocks) return (int)cudaErrorInvalidValue;
     const int bs = C / n_blocks;
     const size_t smem = (size_t)bs * GR_TOK * sizeof(float);
-    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    if (smem > 160 * 1024) return (int)cudaErrorInvalidValue;
+    if (N <= 256) {
+        // few tokens: more and smaller blocks, the inputs of a part shared among a block's warps
+        const size_t smem_few = smem + (size_t)GR_SPLIT * 2 * GR_TOK * 32 * sizeof(float);
+        if (smem_few > 48 * 1024) {
+            const cudaError_t e = cudaFuncSetAttribute(block_gates_few_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                       (int)smem_few);
+            if (e != cudaSuccess) return (int)e;
+        }
+        const dim3 grid_few((N + GR_TOK - 1) / GR_TOK, n_blocks, (bs + 31) / 32);
+        mv_launch(block_gates_few_kernel, grid_few, 32 * GR_SPLIT, smem_few, stream, u, wa_t, wi_t, ba, bi, lam, c, a_out,
+                  x_out, N, C, bs);
+        return mv_launch_status();
+    }
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(block_gates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -116,6 +197,7 @@ gated_recurrence_kernel(const float* __restrict__ a, const float* __restrict__ x
     if (W > 1) {
         float P = 1.f, S = 0.f;
         if (live)
+#pragma unroll 8
             for (int t = t0; t < t1; ++t) {
                 const size_t at = (size_t)(row0 + t) * C + ch;
                 const float d = a[at];
@@ -130,6 +212,7 @@ gated_recurrence_kernel(const float* __restrict__ a, const float* __restrict__ x
     }
     if (!live) return;
     float S = carry;
+#pragma unroll 8
     for (int t = t0; t < t1; ++t) {
         const size_t row = (size_t)(row0 + t);
         S = fmaf(a[row * C + ch], S, x[row * C + ch]);
@@ -144,7 +227,8 @@ MV_API int mv_gated_recurrence(const float* a, const float* x, const float* y, i
                                const int* cu, void* out, int dtype, int n_seqs, int C, int max_len, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (C < 1) return (int)cudaErrorInvalidValue;
-    const dim3 grid((C + 31) / 32, n_seqs), block(32, max_len >= 4 * GR_WARPS ? GR_WARPS : 1);
+    // pieces of 16 tokens at least, 32 pieces at most
+    const dim3 grid((C + 31) / 32, n_seqs), block(32, max_len >= 64 ? min(GR_WARPS, max_len / 16) : 1);
     if (dtype == MV_DT_BF16)
         mv_launch(gated_recurrence_kernel<__nv_bfloat16>, grid, block, 0, stream, a, x, y, ldy, state, slots, cu,
                   (__nv_bfloat16*)out, C);

@@ -47,6 +47,8 @@ def model_numbers(model) -> dict:
         """Operations of one mixer beside its projections over a prompt of T tokens."""
         if hasattr(m, "left") and hasattr(m, "right"):                 # two mixers side by side
             return mixer_flops(m.left, T) + mixer_flops(m.right, T)
+        if hasattr(m, "blocks") and hasattr(m, "width"):               # a gated linear recurrence: its two gate products a part
+            return 4 * m.width * (m.width // m.blocks) * T
         if getattr(m, "chunk", 0):                                     # softmax attention inside chunks of positions
             full, rest = divmod(T, m.chunk)
             pairs = full * m.chunk * (m.chunk + 1) // 2 + rest * (rest + 1) // 2
@@ -62,7 +64,8 @@ def model_numbers(model) -> dict:
         if hasattr(m, "window") and hasattr(m, "dk"):                 # softmax attention, a window and kept first tokens
             reach = m.window + m.keep_first if m.window else T
             pairs = T * (T + 1) // 2 if reach >= T else reach * (reach + 1) // 2 + (T - reach) * reach
-            return 2 * m.nh * (m.dk + m.dv) * pairs
+            # (weights mixed between the heads: one more sum over the heads a weight)
+            return 2 * m.nh * (m.dk + m.dv + (m.nh if getattr(m, "talk", False) else 0)) * pairs
         if hasattr(m, "dk") and hasattr(m, "dv"):                     # a decaying matrix state: update and read-out
             return 5 * m.nh * m.dk * m.dv * T
         return 0

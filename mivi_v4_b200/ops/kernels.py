@@ -578,8 +578,8 @@ def block_gates(u: torch.Tensor, wa_t: torch.Tensor, wi_t: torch.Tensor, ba: tor
     if nb < 1 or C % nb:
         raise KernelError(f"block_gates: {C} channels do not split into {nb} parts")
     bs = C // nb
-    if bs * 64 > 200 * 1024:
-        raise KernelError(f"block_gates: parts of {bs} channels are more than a block holds (3,200)")
+    if bs * 64 > 160 * 1024:
+        raise KernelError(f"block_gates: parts of {bs} channels are more than a block holds (2,560)")
     _check(_fn("core", "mv_block_gates")(
         _need(u, "block_gates input", torch.float32, (N, C)), _need(wa_t, "block_gates A", torch.float32, (nb, bs, bs)),
         _need(wi_t, "block_gates B", torch.float32, (nb, bs, bs)), _need(ba, "block_gates A bias", torch.float32, (C,)),
