@@ -13,7 +13,7 @@
 #include "common.cuh"
 
 #define GR_TOK 16            // tokens a block of the gate kernel holds
-#define GR_WARPS 32          // the most pieces a long sequence is cut into for the walk
+#define GR_THREADS 1024      // channels a block x the most pieces a long sequence is cut into for the walk
 
 __device__ __forceinline__ float gr_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
@@ -41,7 +41,7 @@ block_gates_kernel(const float* __restrict__ u, const float* __restrict__ wa_t, 
     for (int t = 0; t < GR_TOK; ++t) ar[t] = ai[t] = 0.f;
     const float* wa = wa_t + (size_t)b * bs * bs + o;
     const float* wi = wi_t + (size_t)b * bs * bs + o;
-#pragma unroll 2
+#pragma unroll 8
     for (int in = 0; in < bs; ++in) {
         const float x = wa[(size_t)in * bs], y = wi[(size_t)in * bs];
         const float4* row = reinterpret_cast<const float4*>(gr_us + in * GR_TOK);
@@ -174,18 +174,20 @@ __device__ __forceinline__ float gr_gelu_tanh(float z) {
 }
 
 // a, x [N, C] dense; y [N, C] with row stride ldy (the other branch before its activation); state [slots][C];
-// out [N, C] in the model's dtype.  A block is (32 channels, a sequence); blockDim.y warps each walk one piece of
+// out [N, C] in the model's dtype.  A block is (blockDim.x channels, a sequence): 32, or 16 where that is what gives
+// every multiprocessor a block; its blockDim.y rows of threads each walk one piece of
 // the sequence's tokens: first from a zero state, keeping the product of the piece's decays, then, once every
-// piece's (product, end state) is known, again from the state that the pieces before leave.  With one warp
+// piece's (product, end state) is known, again from the state that the pieces before leave.  With one row
 // (steps of few tokens a sequence) the walk is done once.
 template <typename T>
-__global__ void __launch_bounds__(32 * GR_WARPS)
+__global__ void __launch_bounds__(GR_THREADS)
 gated_recurrence_kernel(const float* __restrict__ a, const float* __restrict__ x, const float* __restrict__ y, int ldy,
                         float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu,
                         T* __restrict__ out, int C) {
     mv_pdl_begin();
-    __shared__ float sp[GR_WARPS][32], ss[GR_WARPS][32];
-    const int ch = blockIdx.x * 32 + threadIdx.x, sq = blockIdx.y, w = threadIdx.y, W = blockDim.y;
+    __shared__ float sp[GR_THREADS], ss[GR_THREADS];          // [piece][channel of the block]
+    const int CH = blockDim.x;
+    const int ch = blockIdx.x * CH + threadIdx.x, sq = blockIdx.y, w = threadIdx.y, W = blockDim.y;
     const int row0 = cu[sq], len = cu[sq + 1] - row0;
     if (len <= 0) return;
     const bool live = ch < C;
@@ -204,11 +206,11 @@ gated_recurrence_kernel(const float* __restrict__ a, const float* __restrict__ x
                 S = fmaf(d, S, x[at]);
                 P *= d;
             }
-        sp[w][threadIdx.x] = P;
-        ss[w][threadIdx.x] = S;
+        sp[w * CH + threadIdx.x] = P;
+        ss[w * CH + threadIdx.x] = S;
         __syncthreads();
         if (live)
-            for (int v = 0; v < w; ++v) carry = fmaf(sp[v][threadIdx.x], carry, ss[v][threadIdx.x]);
+            for (int v = 0; v < w; ++v) carry = fmaf(sp[v * CH + threadIdx.x], carry, ss[v * CH + threadIdx.x]);
     }
     if (!live) return;
     float S = carry;
@@ -227,8 +229,10 @@ MV_API int mv_gated_recurrence(const float* a, const float* x, const float* y, i
                                const int* cu, void* out, int dtype, int n_seqs, int C, int max_len, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (C < 1) return (int)cudaErrorInvalidValue;
-    // pieces of 16 tokens at least, 32 pieces at most
-    const dim3 grid((C + 31) / 32, n_seqs), block(32, max_len >= 64 ? min(GR_WARPS, max_len / 16) : 1);
+    // pieces of 16 tokens at least; 32 channels a block and up to 32 pieces, or, where that leaves multiprocessors
+    // without a block in a long step, 16 channels and up to 64 pieces
+    const int ch = (max_len >= 1024 && (long long)((C + 31) / 32) * n_seqs < 120) ? 16 : 32;
+    const dim3 grid((C + ch - 1) / ch, n_seqs), block(ch, max_len >= 64 ? min(GR_THREADS / ch, max_len / 16) : 1);
     if (dtype == MV_DT_BF16)
         mv_launch(gated_recurrence_kernel<__nv_bfloat16>, grid, block, 0, stream, a, x, y, ldy, state, slots, cu,
                   (__nv_bfloat16*)out, C);

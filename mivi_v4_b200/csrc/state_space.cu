@@ -149,6 +149,33 @@ ssm_decode_prepare_kernel(const float* __restrict__ u, int ld, const float* __re
     out[(size_t)b * C + c] = acc / (1.0f + expf(-acc));
 }
 
+// The convolution alone for a step of one token a sequence (row b is sequence b's token): output and the kept inputs'
+// shift in ONE kernel.  A thread is a (sequence, channel): it alone reads and writes that channel's kept inputs.
+template <bool ACT>
+__global__ void __launch_bounds__(256)
+causal_conv_decode_kernel(const float* __restrict__ u, int ld, const float* __restrict__ taps,
+                          const float* __restrict__ bias, float* __restrict__ state, const int* __restrict__ slots,
+                          float* __restrict__ out, int C, int K) {
+    mv_pdl_begin();
+    const int b = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const float x = u[(size_t)b * ld + c];
+    float acc = bias ? bias[c] : 0.f;
+    if (K > 1) {
+        const bool ok = mv_slot_ok(slots[b]);
+        float* st = state + (size_t)mv_read_slot(slots[b]) * (K - 1) * C;
+        for (int j = 0; j < K - 1; ++j) {
+            const float kept = st[(size_t)j * C + c];
+            acc = fmaf(taps[(size_t)c * K + j], kept, acc);
+            if (j > 0 && ok) st[(size_t)(j - 1) * C + c] = kept;
+        }
+        if (ok) st[(size_t)(K - 2) * C + c] = x;
+    }
+    acc = fmaf(taps[(size_t)c * K + K - 1], x, acc);
+    out[(size_t)b * C + c] = ACT ? acc / (1.0f + expf(-acc)) : acc;
+}
+
 MV_GUARD_SETTER(state_space)
 
 // One token a sequence (row b belongs to slots[b]): mv_causal_conv_silu and mv_step_size together.
@@ -165,12 +192,23 @@ MV_API int mv_ssm_decode_prepare(const float* u, int ld, const float* taps, cons
 
 // u: the convolution's input columns [N, C] with row stride ld; taps [C, K]; bias [C] or null; state
 // [slots][K - 1][C]; out [N, C] dense; act: 1 silu on the result, 0 none.  Two kernels: the outputs (which read
-// the kept inputs), then the kept inputs' update.
+// the kept inputs), then the kept inputs' update.  one_each: the caller says that every sequence brings one token and
+// that row b is sequence b's (a decode step); both then happen in one kernel.
 MV_API int mv_causal_conv(const float* u, int ld, const float* taps, const float* bias, float* state,
                           const int* seq_of, const int* cu, const int* slots, float* out, int N, int n_seqs,
-                          int C, int K, int act, cudaStream_t stream) {
+                          int C, int K, int act, int one_each, cudaStream_t stream) {
     if (N <= 0 || n_seqs <= 0) return 0;
     if (K < 1 || K > SP_MAX_TAPS || C < 1) return (int)cudaErrorInvalidValue;
+    if (one_each && N == n_seqs) {
+        // one token a sequence, row b sequence b's: one kernel
+        if (act)
+            mv_launch(causal_conv_decode_kernel<true>, dim3((C + 255) / 256, n_seqs), 256, 0, stream, u, ld, taps, bias, state,
+                      slots, out, C, K);
+        else
+            mv_launch(causal_conv_decode_kernel<false>, dim3((C + 255) / 256, n_seqs), 256, 0, stream, u, ld, taps, bias, state,
+                      slots, out, C, K);
+        return mv_launch_status();
+    }
     const long long total = (long long)N * C;
     const bool wide = C % 4 == 0 && ld % 4 == 0 && N >= 64 &&
                       (((uintptr_t)u | (uintptr_t)bias | (uintptr_t)state | (uintptr_t)out | (uintptr_t)taps) & 15) == 0;
@@ -195,7 +233,7 @@ MV_API int mv_causal_conv(const float* u, int ld, const float* taps, const float
 MV_API int mv_causal_conv_silu(const float* u, int ld, const float* taps, const float* bias, float* state,
                                const int* seq_of, const int* cu, const int* slots, float* out, int N, int n_seqs,
                                int C, int K, cudaStream_t stream) {
-    return mv_causal_conv(u, ld, taps, bias, state, seq_of, cu, slots, out, N, n_seqs, C, K, 1, stream);
+    return mv_causal_conv(u, ld, taps, bias, state, seq_of, cu, slots, out, N, n_seqs, C, K, 1, 0, stream);
 }
 
 // raw [N, H] with row stride ld; dt_bias, a_log [H]; log_a, b_out [N, H] dense.

@@ -74,7 +74,7 @@ _SIGNATURES = {
         "mv_scalar_scan_chunked": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _I,
                                    _I, _I, _I, _I, _I, _P],
         "mv_memory_gates": [_P, _I, _P, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _P],
-        "mv_causal_conv": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "mv_causal_conv": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
         "mv_ssm_decode_prepare": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P],
         "mv_step_size": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
         "mv_route": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
@@ -682,14 +682,17 @@ def memory_gates(zi: torch.Tensor, zf: torch.Tensor, bi: torch.Tensor, bf: torch
 
 def causal_conv(u: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
                 seq_of: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, n_seqs: int,
-                act: bool = False) -> torch.Tensor:
+                act: bool = False, one_each: bool = False) -> torch.Tensor:
     """out = bias + sum_j taps[:, j] * u[t - (K - 1) + j] per channel along each sequence (the last tap is the
     current token's; zeros before a sequence's start), float32; with ``act`` silu of that.  ``u`` [N, C] may be a
-    column slice; ``state`` [slots, K - 1, C] holds each sequence's last K - 1 inputs and is brought up to date."""
+    column slice; ``state`` [slots, K - 1, C] holds each sequence's last K - 1 inputs and is brought up to date.
+    ``one_each``: every sequence brings one token and row b is sequence b's (a decode step): output and kept inputs in
+    one kernel."""
     N, C = out.shape
     K = taps.shape[1]
     if not 1 <= K <= MAX_CONV_K:
         raise KernelError(f"causal_conv: {K} taps are outside 1..{MAX_CONV_K}")
+    one_each = bool(one_each) and N == int(n_seqs)
     up, ldu = _cols(u, "causal_conv input", N, C)
     if K > 1:
         _guard("core", "state_space", out.device, n_slots=state.shape[0])
@@ -697,15 +700,19 @@ def causal_conv(u: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor
         up, ldu, _need(taps, "conv taps", torch.float32, (C, K)), _need(bias, "conv bias", torch.float32, (C,), True),
         _need(state, "conv state", torch.float32, (None, max(K - 1, 0), C)) if K > 1 else None,
         _need(seq_of, "seq_of", torch.int32), _need(cu, "cu", torch.int32), _need(slots, "slots", torch.int32),
-        _need(out, "causal_conv out", torch.float32), N, int(n_seqs), C, K, int(bool(act)), _stream()), "mv_causal_conv")
+        _need(out, "causal_conv out", torch.float32), N, int(n_seqs), C, K, int(bool(act)), int(one_each), _stream()),
+        "mv_causal_conv")
+    if one_each or K == 1:
+        add_launches(-1)                     # one kernel, not the two that a call is counted as
     account(N * C * 8 + 2 * n_seqs * (K - 1) * C * 4, 2 * N * C * K)
     return out
 
 
 def causal_conv_silu(u: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
-                     seq_of: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, n_seqs: int) -> torch.Tensor:
+                     seq_of: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, n_seqs: int,
+                     one_each: bool = False) -> torch.Tensor:
     """:func:`causal_conv` followed by silu."""
-    return causal_conv(u, taps, bias, state, seq_of, cu, slots, out, n_seqs, act=True)
+    return causal_conv(u, taps, bias, state, seq_of, cu, slots, out, n_seqs, act=True, one_each=one_each)
 
 
 def step_size(raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, log_a: torch.Tensor, b: torch.Tensor) -> None:

@@ -415,7 +415,7 @@ class SinkAttention(Part):
         if self.conv:
             rows = self.scratch(step, "qk", (N, (nh + nkv) * dk), torch.float32)
             K.causal_conv(proj[:, :(nh + nkv) * dk], self.taps, None, conv_state, step.seq_of, step.cu, step.slots, rows,
-                          step.n_seqs)
+                          step.n_seqs, one_each=step.is_decode)
         K.qkv_prepare_wide(rows, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.rot_dims,
                            rot[0] if rot is not None else None, step.positions, step.seq_of, view.page_table,
                            view.pool, view.page_size, q, nh, nkv, dk, 0 if self.values_are_keys else dv,
@@ -914,7 +914,8 @@ class GatedRecurrence(Part):
         proj = self.scratch(step, "proj", (N, self.w_yx.shape[0]), torch.float32)
         linear(u, self.w_yx, proj, bias=self.b_yx)
         uc = self.scratch(step, "u", (N, C), torch.float32)
-        K.causal_conv(proj[:, C:2 * C], self.taps, self.b_conv, conv_state, step.seq_of, step.cu, step.slots, uc, step.n_seqs)
+        K.causal_conv(proj[:, C:2 * C], self.taps, self.b_conv, conv_state, step.seq_of, step.cu, step.slots, uc, step.n_seqs,
+                      one_each=step.is_decode)
         a = self.scratch(step, "a", (N, C), torch.float32)
         x = self.scratch(step, "x", (N, C), torch.float32)
         K.block_gates(uc, self.wa_t, self.wi_t, self.ba, self.bi, self.lam, self.c, a, x)
@@ -979,7 +980,8 @@ class GatedDeltaRule(Part):
         proj = self.scratch(step, "proj", (N, self.w_in.shape[0]), torch.float32)
         linear(u, self.w_in, proj)
         xbc = self.scratch(step, "xbc", (N, C), torch.float32)
-        K.causal_conv_silu(proj[:, :C], self.taps, None, conv_state, step.seq_of, step.cu, step.slots, xbc, step.n_seqs)
+        K.causal_conv_silu(proj[:, :C], self.taps, None, conv_state, step.seq_of, step.cu, step.slots, xbc, step.n_seqs,
+                           one_each=step.is_decode)
         b0 = C + vv
         o = self.scratch(step, "o", (N, vv), torch.float32)
         K.delta_scan(xbc[:, :qk], xbc[:, qk:2 * qk], xbc[:, 2 * qk:], proj[:, b0:b0 + nh], proj[:, b0 + nh:b0 + 2 * nh],

@@ -311,6 +311,32 @@ def test_causal_convolution_without_activation_under_every_cut(C, taps, bias, ac
         assert (state[[0, 2]] == 5.0).all()
 
 
+@pytest.mark.parametrize("C,taps,act", [(48, 4, False), (30, 1, False), (7, 3, True), (300, 2, False)])
+def test_causal_convolution_of_a_decode_batch_in_one_kernel(C, taps, act):
+    """Three sequences, a token each a step (row b is sequence b's), their slots in no order, after a prompt of their own."""
+    k_ = K()
+    r = _r(C * taps)
+    lens, w, b = [9, 1, 14], r(C, taps), r(C)
+    xs = [r(n + 6, C) for n in lens]
+    wants = [P.silu(P.causal_conv(x, w, b)) if act else P.causal_conv(x, w, b) for x in xs]
+    state = torch.full((5, max(taps - 1, 1), C), 5.0, device=DEV)
+    slots = [3, 0, 4]
+    state[slots] = 0.0
+    st = state if taps > 1 else None
+    cu = [0, lens[0], lens[0] + lens[1], sum(lens)]
+    seq_of = [i for i, n in enumerate(lens) for _ in range(n)]
+    o = torch.full((sum(lens), C), float("nan"), device=DEV)
+    k_.causal_conv(dev(torch.cat([x[:n] for x, n in zip(xs, lens)])), dev(w), dev(b), st, i32(seq_of), i32(cu), i32(slots), o, 3, act=act)
+    for i, n in enumerate(lens):
+        close(o[cu[i]:cu[i + 1]], wants[i][:n], 2e-6, f"prompt {i}")
+    for t in range(6):
+        o = torch.full((3, C), float("nan"), device=DEV)
+        k_.causal_conv(dev(torch.stack([x[n + t] for x, n in zip(xs, lens)])), dev(w), dev(b), st, i32([0, 1, 2]), i32([0, 1, 2, 3]),
+                       i32(slots), o, 3, act=act, one_each=True)
+        close(o, torch.stack([wt[n + t] for wt, n in zip(wants, lens)]), 2e-6, f"token {t}")
+    assert (state[[1, 2]] == 5.0).all()
+
+
 # ------------------------------------------------------------------------------------------ gated linear recurrence
 def _recurrence_case(T, C, nb, seed):
     r = _r(seed)
