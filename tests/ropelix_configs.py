@@ -85,6 +85,16 @@ ROP_D = {"architecture": "Ropelix", "vocab": 77, "width": 40, "norm": {"eps": 1e
                     _parallel(_left(2, 1, 8, 8, 1, 2, 10.0, 0.5, 2.0), 24, 3, 2, 0.2, 1.5, _dense(24, 1.0)),
                     _delta(4, 1, 8, 8, 4, _dense(24, 0.5))]}
 
+# E: the attention with convolved keys first; eight heads on four kv heads beside a recurrence of four parts; heads of
+#    80 without a window; windows of 48, 100 and 300; a rotation of no element; long prompts run on it
+ROP_E = {"architecture": "Ropelix", "vocab": 311, "width": 192, "norm": {"eps": 1e-5}, "embedding": {"scale": 4.0},
+         "residual_mult": 0.6,
+         "layers": [_attention(6, 2, 32, 100, 4, 0.18, _dense(160, 2.0)),
+                    _parallel(_left(8, 4, 32, 64, 48, 16, 10000.0, 0.18, 40.0), 96, 4, 2, 0.8, 0.7, _dense(224, 1.5)),
+                    _delta(4, 4, 64, 32, 2, _dense(96, 4.0)),
+                    _attention(2, 1, 80, 0, 2, 0.11, None),
+                    _parallel(_left(3, 3, 48, 48, 300, 0, 0.0, 0.14, 0.0), 120, 3, 3, 0.4, 1.1, _dense(64, 1.0))]}
+
 CONFIGS = {"A": (ROP_A, 41), "B": (ROP_B, 42), "C": (ROP_C, 43), "D": (ROP_D, 44)}
 
 

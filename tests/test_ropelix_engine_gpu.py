@@ -206,3 +206,38 @@ def test_long_steps_and_batches_of_long_prompts(name, dtype, tmp_path):
         at += len(r)
         eng.close(sl)
     eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompts_far_keys_and_decoding_after_them(dtype, tmp_path):
+    """Prompts of several hundred tokens on a fifth configuration: whole, in two unequal portions, and as a batch of
+    three that is then decoded together for 40 tokens, the shortest request ending first."""
+    cfg, seed = RC.ROP_E, 45
+    folder = write_ropelix(tmp_path, cfg, seed)
+    eng = engine_for(folder, dtype, max_tokens=4096, max_batch=4)
+    toks = prompts(cfg["vocab"], [700], seed)[0]
+    want = plain(folder, toks)
+    s = eng.open()
+    assert_rows(eng.step([(s, toks)], "all"), want, dtype, "whole", folder, toks)
+    eng.close(s)
+    s = eng.open()
+    got = torch.cat([eng.step([(s, toks[:437])], "all"), eng.step([(s, toks[437:])], "all")])
+    eng.close(s)
+    assert_rows(got, want, dtype, "two portions", folder, toks)
+    reqs = prompts(cfg["vocab"], [340, 75, 521], seed + 1)
+    n_prompt = [len(r) - 40 for r in reqs[:2]] + [len(reqs[2]) - 25]
+    slots = [eng.open() for _ in reqs]
+    out = eng.step([(sl, r[:n]) for sl, r, n in zip(slots, reqs, n_prompt)], "all")
+    got, at = [[] for _ in reqs], 0
+    for i, n in enumerate(n_prompt):
+        got[i].append(out[at:at + n])
+        at += n
+    for step in range(40):
+        live = [i for i in range(3) if n_prompt[i] + step < len(reqs[i])]
+        out = eng.step([(slots[i], [reqs[i][n_prompt[i] + step]]) for i in live], "last")
+        for j, i in enumerate(live):
+            got[i].append(out[j:j + 1])
+    for i, r in enumerate(reqs):
+        assert_rows(torch.cat(got[i]), plain(folder, r), dtype, f"request {i}", folder, r)
+        eng.close(slots[i])
+    eng.cache.check()
