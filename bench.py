@@ -253,14 +253,14 @@ def ropelix_config(width, layers, heads, kv_heads, ff, vocab):
     q and k whose values are its keys, then a delta-rule layer, and so on; every layer carries a dense clamped
     feed-forward.  The side-by-side attention has a quarter of the kv heads (every head's weights meet every kv
     head's values there)."""
-    left = {"heads": heads, "kv_heads": max(1, kv_heads // 4), "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 50.0,
+    left = {"heads": heads, "kv_heads": max(1, kv_heads // 4), "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 30.0,
             "mask": {"size": 1024}, "rot": {"dims": 32, "base": 1000000.0}}
-    par = {"left": left, "right": {"width": width, "blocks": max(1, width // 256), "conv": 4}, "left_scale": 0.6, "right_scale": 0.5}
-    att = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "conv": 3, "scale": 0.125, "mask": {"size": 1024}}
+    par = {"left": left, "right": {"width": width, "blocks": max(1, width // 256), "conv": 4}, "left_scale": 1.0, "right_scale": 1.0}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "conv": 4, "scale": 0.125, "mask": {"size": 1024}}
     delta = {"heads": max(1, width // 128), "kv_heads": max(1, width // 256), "dim": 128, "vdim": 128, "conv": 4}
     kinds = (("parallel", par), ("attention", att), ("delta", delta))
     return {"architecture": "Ropelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": float(width) ** 0.5},
-            "residual_mult": 0.7,
+            "residual_mult": 0.5,
             "layers": [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}}
                        for i in range(layers)]}
 

@@ -71,7 +71,7 @@ ROP_B = {"architecture": "Ropelix", "vocab": 131, "width": 48, "norm": {"eps": 1
 #    page exactly, eight heads on two and on eight kv heads, a rotation of all of a head, 3 taps
 ROP_C = {"architecture": "Ropelix", "vocab": 200, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 3.5},
          "residual_mult": 0.5,
-         "layers": [_parallel(_left(8, 2, 64, 48, 64, 64, 20000.0, 0.125, 30.0), 96, 3, 3, 0.5, 0.6, _dense(64, 1.5)),
+         "layers": [_parallel(_left(8, 2, 64, 48, 64, 64, 30000.0, 0.11, 30.0), 96, 3, 3, 0.5, 0.65, _dense(64, 1.75)),
                     _delta(2, 1, 72, 40, 4, _dense(96, 1.2)),
                     _attention(8, 8, 48, 64, 3, 0.15, _dense(32, 2.5)),
                     _delta(1, 1, 136, 17, 2, None),
