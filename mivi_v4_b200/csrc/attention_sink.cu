@@ -156,7 +156,20 @@ MV_API int mv_qkv_prepare_wide(const float* proj, int ld, const float* wq, const
 // order, so a position's result depends on nothing but its keys.
 #define AS_WARPS 8
 #define AS_ACC (AS_MAX_DIM / 32)
-template <typename T, bool VEC, int GT>
+// Which element of a value row a lane's r-th sum belongs to: lane + 32 r, or with PAIR (rows of an even length on even
+// offsets) the lane's r/2-th PAIR of neighbours, 2 lane + 64 (r / 2) + (r mod 2), which it loads with one instruction.
+template <bool PAIR> __device__ __forceinline__ int as_dim(int lane, int r) {
+    return PAIR ? 2 * lane + 64 * (r >> 1) + (r & 1) : lane + 32 * r;
+}
+__device__ __forceinline__ void as_load2(const float* p, float& a, float& b) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    a = v.x; b = v.y;
+}
+__device__ __forceinline__ void as_load2(const __nv_bfloat16* p, float& a, float& b) {
+    const unsigned v = *reinterpret_cast<const unsigned*>(p);
+    a = __uint_as_float(v << 16); b = __uint_as_float(v & 0xffff0000u);
+}
+template <typename T, bool VEC, int GT, bool PAIR>
 __global__ void __launch_bounds__(AS_WARPS * 32)
 attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long long page_stride,
                       const int* __restrict__ page_table, int table_stride, int page_shift,
@@ -284,17 +297,39 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
             for (int i = 0; i < GT; ++i)
 #pragma unroll
                 for (int e = 0; e < 8; ++e) pj[i][e] = __shfl_sync(0xffffffffu, p[i], j0 + e);
+            if (PAIR) {
 #pragma unroll
-            for (int r = 0; r < AS_ACC; ++r) {
-                const int d = lane + 32 * r;
-                if (d < dv) {
-                    float x[8];
+                for (int r = 0; r < AS_ACC; r += 2) {
+                    const int d = as_dim<true>(lane, r);
+                    if (d < dv) {
+                        float x0[8], x1[8];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) x[e] = (j0 + e < cnt) ? mv_to_f32(vrow[e][d]) : 0.f;
+                        for (int e = 0; e < 8; ++e) {
+                            x0[e] = x1[e] = 0.f;
+                            if (j0 + e < cnt) as_load2(vrow[e] + d, x0[e], x1[e]);
+                        }
 #pragma unroll
-                    for (int i = 0; i < GT; ++i)
+                        for (int i = 0; i < GT; ++i)
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) acc[i][r] = fmaf(pj[i][e], x[e], acc[i][r]);
+                            for (int e = 0; e < 8; ++e) {
+                                acc[i][r] = fmaf(pj[i][e], x0[e], acc[i][r]);
+                                acc[i][r + 1] = fmaf(pj[i][e], x1[e], acc[i][r + 1]);
+                            }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < AS_ACC; ++r) {
+                    const int d = lane + 32 * r;
+                    if (d < dv) {
+                        float x[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) x[e] = (j0 + e < cnt) ? mv_to_f32(vrow[e][d]) : 0.f;
+#pragma unroll
+                        for (int i = 0; i < GT; ++i)
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) acc[i][r] = fmaf(pj[i][e], x[e], acc[i][r]);
+                    }
                 }
             }
         }
@@ -306,7 +341,7 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
         if (lane == 0) { part_m[wib * GT + i] = m[i]; part_l[wib * GT + i] = l[i]; }
 #pragma unroll
         for (int r = 0; r < AS_ACC; ++r) {
-            const int d = lane + 32 * r;
+            const int d = as_dim<PAIR>(lane, r);
             if (d < dv) part_acc[(wib * GT + i) * dv + d] = acc[i][r];
         }
     }
@@ -359,10 +394,21 @@ MV_API int mv_attention_sink(const void* q, const void* pool, long long page_str
     const int esize = dtype == MV_DT_BF16 ? 2 : 4;
     const bool vec = dk % 8 == 0 && ((uintptr_t)pool % 16) == 0 && (page_stride * esize) % 16 == 0;
     const size_t smem = sizeof(float) * ((size_t)gt * dk + (size_t)AS_WARPS * gt * (dv + 2));
+    // value rows of an even length on even offsets: a lane takes pairs of neighbours, one load each
+    const bool pair = dv % 2 == 0 && (v_in_k ? dk : dv) % 2 == 0 && page_stride % 2 == 0 && ((uintptr_t)pool % 8) == 0 &&
+                      ((long long)nkv * page_size * dk) % 2 == 0;
 #define AS_LAUNCH(T, V, GTV)                                                                                         \
-    mv_launch(attention_sink_kernel<T, V, GTV>, blocks, AS_WARPS * 32, smem, stream, (const T*)q, (const T*)pool,    \
+    do {                                                                                                             \
+    if (pair)                                                                                                        \
+        mv_launch(attention_sink_kernel<T, V, GTV, true>, blocks, AS_WARPS * 32, smem, stream, (const T*)q,          \
+                  (const T*)pool, page_stride, page_table, table_stride, page_shift, positions, seq_of, sinks, gate, \
+                  ld_gate, (T*)o, N, nh, nkv, dk, dv, scale, cap, window, keep_first, chunk, r1, r2, v_in_k,         \
+                  gate_wide, o_all);                                                                                 \
+    else                                                                                                             \
+    mv_launch(attention_sink_kernel<T, V, GTV, false>, blocks, AS_WARPS * 32, smem, stream, (const T*)q, (const T*)pool,    \
               page_stride, page_table, table_stride, page_shift, positions, seq_of, sinks, gate, ld_gate, (T*)o, N,  \
-              nh, nkv, dk, dv, scale, cap, window, keep_first, chunk, r1, r2, v_in_k, gate_wide, o_all)
+              nh, nkv, dk, dv, scale, cap, window, keep_first, chunk, r1, r2, v_in_k, gate_wide, o_all);             \
+    } while (0)
 #define AS_PICK(T, V)                                                                                                \
     do {                                                                                                             \
         if (gt == 4) AS_LAUNCH(T, V, 4); else if (gt == 2) AS_LAUNCH(T, V, 2); else AS_LAUNCH(T, V, 1);             \
