@@ -268,10 +268,64 @@ __global__ void scaled_add_norm_kernel(const float* __restrict__ y1, float s1, c
     for (int h = threadIdx.x; h < H; h += blockDim.x) out[base + h] = mv_from_f32<TO>(resid[base + h] * scale * w[h]);
 }
 
+// The same with four values a load, a row's values kept in registers between the two passes: for rows of a
+// multiple of 4 and at most 8 values a thread, 16-byte aligned.
+template <typename TO>
+__global__ void __launch_bounds__(512)
+scaled_add_norm_vec_kernel(const float* __restrict__ y1, float s1, const float* __restrict__ y2, float s2,
+                           const float* __restrict__ vec, float* __restrict__ resid, const float* __restrict__ w, float eps,
+                           TO* __restrict__ out, int H) {
+    mv_pdl_begin();
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * H;
+    const int H4 = H >> 2;
+    float4 r[2];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int h4 = threadIdx.x + i * blockDim.x;
+        r[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (h4 < H4) {
+            const float4 a = reinterpret_cast<const float4*>(y1 + base)[h4];
+            float4 v = make_float4(s1 * a.x, s1 * a.y, s1 * a.z, s1 * a.w);
+            if (y2) {
+                const float4 b = reinterpret_cast<const float4*>(y2 + base)[h4];
+                v = make_float4(fmaf(s2, b.x, v.x), fmaf(s2, b.y, v.y), fmaf(s2, b.z, v.z), fmaf(s2, b.w, v.w));
+            }
+            const float4 c = reinterpret_cast<const float4*>(vec)[h4];
+            const float4 x = reinterpret_cast<const float4*>(resid + base)[h4];
+            r[i] = make_float4(fmaf(c.x, v.x, x.x), fmaf(c.y, v.y, x.y), fmaf(c.z, v.z, x.z), fmaf(c.w, v.w, x.w));
+            reinterpret_cast<float4*>(resid + base)[h4] = r[i];
+            ss = fmaf(r[i].x, r[i].x, ss); ss = fmaf(r[i].y, r[i].y, ss);
+            ss = fmaf(r[i].z, r[i].z, ss); ss = fmaf(r[i].w, r[i].w, ss);
+        }
+    }
+    if (!w) return;
+    const float scale = 1.0f / sqrtf(mv_block_sum(ss, scratch) / (float)H + eps);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int h4 = threadIdx.x + i * blockDim.x;
+        if (h4 < H4) {
+            const float4 ww = reinterpret_cast<const float4*>(w)[h4];
+            mv_store4(out + base + 4 * (size_t)h4, r[i].x * scale * ww.x, r[i].y * scale * ww.y, r[i].z * scale * ww.z,
+                      r[i].w * scale * ww.w);
+        }
+    }
+}
+
 MV_API int mv_scaled_add_norm(const float* y1, float s1, const float* y2, float s2, const float* vec, float* resid,
                               const float* w, float eps, void* out, int out_dtype, int N, int H, cudaStream_t stream) {
     if (N <= 0) return 0;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    const bool aligned = (((uintptr_t)y1 | (uintptr_t)y2 | (uintptr_t)vec | (uintptr_t)resid | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
+    if (H % 4 == 0 && H / 4 <= 2 * threads && aligned) {
+        if (out_dtype == MV_DT_BF16)
+            mv_launch(scaled_add_norm_vec_kernel<__nv_bfloat16>, N, threads, 0, stream, y1, s1, y2, s2, vec, resid, w, eps,
+                      (__nv_bfloat16*)out, H);
+        else
+            mv_launch(scaled_add_norm_vec_kernel<float>, N, threads, 0, stream, y1, s1, y2, s2, vec, resid, w, eps, (float*)out, H);
+        return mv_launch_status();
+    }
     if (out_dtype == MV_DT_BF16)
         mv_launch(scaled_add_norm_kernel<__nv_bfloat16>, N, threads, 0, stream, y1, s1, y2, s2, vec, resid, w, eps,
                   (__nv_bfloat16*)out, H);
@@ -340,10 +394,42 @@ __global__ void glu_clamped_kernel(const float* __restrict__ gu, TO* __restrict_
     h[i] = mv_from_f32<TO>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
 }
 
+// The same with four consecutive features a thread (16-byte loads): F a multiple of 4, 16-byte aligned rows.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+glu_clamped_vec_kernel(const float* __restrict__ gu, TO* __restrict__ h, long long total4, int F, float limit, float alpha) {
+    mv_pdl_begin();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total4) return;
+    const int F4 = F >> 2;
+    const long long n = i / F4;
+    const int f = (int)(i - n * F4) << 2;
+    const float4 g4 = *reinterpret_cast<const float4*>(gu + n * 2 * F + f);
+    const float4 u4 = *reinterpret_cast<const float4*>(gu + n * 2 * F + F + f);
+    const float gs[4] = {g4.x, g4.y, g4.z, g4.w}, us[4] = {u4.x, u4.y, u4.z, u4.w};
+    float y[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float g = fminf(gs[j], limit);
+        const float u = fminf(fmaxf(us[j], -limit), limit);
+        y[j] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    }
+    mv_store4(h + n * F + f, y[0], y[1], y[2], y[3]);
+}
+
 MV_API int mv_glu_clamped(const float* gu, void* h, int h_dtype, int N, int F, float limit, float alpha,
                           cudaStream_t stream) {
     const long long total = (long long)N * F;
     if (total <= 0) return 0;
+    if (F % 4 == 0 && (((uintptr_t)gu | (uintptr_t)h) & 15) == 0) {
+        const unsigned blocks4 = (unsigned)((total / 4 + 255) / 256);
+        if (h_dtype == MV_DT_BF16)
+            mv_launch(glu_clamped_vec_kernel<__nv_bfloat16>, blocks4, 256, 0, stream, gu, (__nv_bfloat16*)h, total / 4, F, limit,
+                      alpha);
+        else
+            mv_launch(glu_clamped_vec_kernel<float>, blocks4, 256, 0, stream, gu, (float*)h, total / 4, F, limit, alpha);
+        return mv_launch_status();
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (h_dtype == MV_DT_BF16)
         mv_launch(glu_clamped_kernel<__nv_bfloat16>, blocks, 256, 0, stream, gu, (__nv_bfloat16*)h, total, F, limit, alpha);

@@ -463,7 +463,7 @@ def test_delta_rule_with_a_decay_a_head_under_every_cut(H, KV, dk, dv):
 
 # ------------------------------------------------------------------------------------------ joining kernel and norm
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H", [48, 200, 1030, 2048])
+@pytest.mark.parametrize("H", [48, 200, 1030, 2048, 4100])
 def test_scaled_add_norm(H, out_dtype):
     k_ = K()
     r = _r(H)
@@ -494,3 +494,17 @@ def test_norm_part_with_a_weight_around_zero():
     part.load({"weight": dev(w)})
     part.forward(dev(x), out)
     close(out, P.rms_norm(x, w, 1e-5), 2e-6)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("F", [33, 48, 320, 1028])
+def test_clamped_activation_four_features_a_thread_and_one(F, out_dtype):
+    k_ = K()
+    r = _r(F)
+    N = 7
+    gu = 3.0 * r(N, 2 * F)
+    eye, zero = torch.eye(F, dtype=F64), torch.zeros(F, F, dtype=F64)
+    want = P.clamped_glu(gu, {"gate": torch.cat([eye, zero], 1), "up": torch.cat([zero, eye], 1), "down": eye}, {"limit": 1.25})
+    out = torch.full((N, F), float("nan"), dtype=out_dtype, device=DEV)
+    k_.glu_clamped(dev(gu), out, 1.25, 1.702)
+    close(out, want, 2e-6 if out_dtype == torch.float32 else 5e-3)
